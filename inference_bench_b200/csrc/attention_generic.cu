@@ -23,9 +23,13 @@ __global__ void qk_norm_rope_kv_kernel(const float* __restrict__ qkv, int P, siz
                                        const float* __restrict__ k_norm_w, float eps, const float* __restrict__ cos_t,
                                        const float* __restrict__ sin_t, int rot_half, const int* __restrict__ positions,
                                        const int* __restrict__ seg_of_token, A* __restrict__ q_out, IbKvView kv, int write_kv, int T,
-                                       int heads, unsigned* __restrict__ status, const float* __restrict__ bias, int qk_dim, int v_dim) {
+                                       int heads, unsigned* __restrict__ status, const float* __restrict__ bias, int qk_dim, int v_dim, int row, int q_col,
+                                       int k_col, int v_col, int unit_norm_after) {
   // qk_dim, v_dim: sizes of a query/key head and of a value head (both at most the cache's row, kv.head_dim); the projection's row is
   // [heads x qk_dim | kv_heads x qk_dim | kv_heads x v_dim]. bias: one value per entry of that row, or null.
+  // row > 0: the projection's row has `row` entries and the three parts start at q_col, k_col, v_col; v_col < 0: the values are the keys
+  // as projected (with their bias, before any norm or rotation). unit_norm_after: q and k are divided by their root mean square over
+  // the head after the rotation, without weights (q_norm_w and k_norm_w are then not read).
   __shared__ float vec[kWarps][kMaxHeadDim];
   ib::pdl_launch_dependents();
   ib::pdl_wait();
@@ -35,11 +39,12 @@ __global__ void qk_norm_rope_kv_kernel(const float* __restrict__ qkv, int P, siz
   long long item = (long long)blockIdx.x * kWarps + warp;
   if (item >= (long long)T * slots) return;
   const int t = (int)(item / slots), j = (int)(item % slots);
-  const int R = (heads + kvh) * qk_dim + kvh * v_dim;
+  const int R = row > 0 ? row : (heads + kvh) * qk_dim + kvh * v_dim;
   const bool is_q = j < heads, is_k = !is_q && j < heads + kvh;
   if (!is_q && !write_kv) return;
   const int hd = (is_q || is_k) ? qk_dim : v_dim;
-  const int col0 = (is_q || is_k) ? j * qk_dim : (heads + kvh) * qk_dim + (j - heads - kvh) * v_dim;
+  int col0 = (is_q || is_k) ? j * qk_dim : (heads + kvh) * qk_dim + (j - heads - kvh) * v_dim;
+  if (row > 0) col0 = is_q ? q_col + j * qk_dim : (is_k ? k_col + (j - heads) * qk_dim : (v_col < 0 ? k_col + (j - heads - kvh) * qk_dim : v_col + (j - heads - kvh) * v_dim));
   const float* src = qkv + (size_t)t * R + col0;
   float* v = vec[warp];
   float ss = 0.f;
@@ -51,7 +56,7 @@ __global__ void qk_norm_rope_kv_kernel(const float* __restrict__ qkv, int P, siz
     ss += a * a;
   }
   __syncwarp();
-  const float* nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+  const float* nw = unit_norm_after ? nullptr : (is_q ? q_norm_w : (is_k ? k_norm_w : nullptr));
   if (nw) {
     ss = ib::warp_sum(ss);
     float inv = rsqrtf(ss / (float)hd + eps);
@@ -66,6 +71,14 @@ __global__ void qk_norm_rope_kv_kernel(const float* __restrict__ qkv, int P, siz
       v[d] = a * c - b * s;
       v[d + rot_half] = b * c + a * s;
     }
+    __syncwarp();
+  }
+  if ((is_q || is_k) && unit_norm_after) {
+    float s2 = 0.f;
+    for (int d = lane; d < hd; d += 32) s2 = __fmaf_rn(v[d], v[d], s2);
+    s2 = ib::warp_sum(s2);
+    const float inv = 1.f / sqrtf(s2 / (float)hd + eps);
+    for (int d = lane; d < hd; d += 32) v[d] *= inv;
     __syncwarp();
   }
   if (is_q) {
@@ -203,9 +216,15 @@ __global__ void qk_norm_rope_kv_vec_kernel(const float* __restrict__ qkv, int P,
 template <typename A, typename C>
 __global__ void attention_generic_kernel(const A* __restrict__ q, IbKvView kv, const int* __restrict__ positions,
                                          const int* __restrict__ seg_of_token, int window, float scale, A* __restrict__ out, int T,
-                                         int heads, unsigned* __restrict__ status, int qk_dim, int v_dim, float softcap, int sink) {
+                                         int heads, unsigned* __restrict__ status, int qk_dim, int v_dim, float softcap, int sink, int chunk,
+                                         const float* __restrict__ sink_values, const float* __restrict__ gate, int gate_P, size_t gate_stride, int gate_row,
+                                         float out_scale, int out_row) {
   // qk_dim, v_dim: a query/key head's and a value head's size (at most the cache's row). softcap > 0: s <- softcap * tanh(s / softcap).
-  // sink: the softmax has one more term whose score is 0 and which has no value (its denominator is 1 + sum exp(s)).
+  // sink: the softmax has one more term whose score is 0 and which has no value (its denominator is 1 + sum exp(s)); with sink_values
+  // the term's score is sink_values[head] instead (not scaled). chunk > 0: a position sees the earlier positions of its own block of
+  // `chunk` positions, counted from position 0 (window is then not read). gate: float32 partial sums [gate_P][T][gate_row], offset to
+  // the first head's column: head h's output is multiplied by sigmoid(gate[t][h]). out_scale multiplies every output; out_row: entries
+  // of an output row (the heads' outputs are its first heads * v_dim).
   __shared__ float qs[kWarps][kMaxHeadDim];
   ib::pdl_launch_dependents();
   ib::pdl_wait();
@@ -216,14 +235,14 @@ __global__ void attention_generic_kernel(const A* __restrict__ q, IbKvView kv, c
   const int t = (int)(item / heads), h = (int)(item % heads);
   const int kvhead = h / (heads / kv.kv_heads);
   const int pos = positions[t], seg = seg_of_token[t];
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo = chunk > 0 ? pos - pos % chunk : (window > 0 ? max(0, pos - window + 1) : 0);
   const A* qrow = q + (size_t)t * heads * hd + (size_t)h * hd;
   for (int d = lane; d < hd; d += 32) qs[warp][d] = ib::to_f32<A>(qrow[d]);
   __syncwarp();
   float acc[kMaxHeadDim / 32];
 #pragma unroll
   for (int r = 0; r < kMaxHeadDim / 32; r++) acc[r] = 0.f;
-  float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;   // the sink is a key of score 0: it starts the running maximum and sum
+  float m = sink ? (sink_values ? sink_values[h] : 0.f) : -INFINITY, l = sink ? 1.f : 0.f;   // the sink is a key of its own score: it starts the running maximum and sum
   (void)row;
   const C* base = (const C*)kv.base;
   for (int k0 = lo; k0 <= pos; k0 += 32) {
@@ -263,8 +282,14 @@ __global__ void attention_generic_kernel(const A* __restrict__ q, IbKvView kv, c
     }
     m = m_new;
   }
-  float inv = l > 0.f ? 1.f / l : 0.f;
-  A* orow = out + (size_t)t * heads * v_dim + (size_t)h * v_dim;
+  float inv = (l > 0.f ? 1.f / l : 0.f) * out_scale;
+  if (gate) {
+    const float* gr = gate + (size_t)t * gate_row + h;
+    float g = gr[0];
+    for (int p = 1; p < gate_P; p++) g += gr[p * gate_stride];
+    inv *= 1.f / (1.f + expf(-g));
+  }
+  A* orow = out + (size_t)t * out_row + (size_t)h * v_dim;
 #pragma unroll
   for (int r = 0; r < kMaxHeadDim / 32; r++) {
     int d = lane + 32 * r;
@@ -288,8 +313,9 @@ int check_view(const char* name, const IbKvView* kv, int heads) {
 extern "C" int ib_qk_norm_rope_kv(const float* qkv, int P, long long stride_p, const float* q_norm_w, const float* k_norm_w, float eps,
                                   const float* cos_t, const float* sin_t, int rot_half, const int* positions, const int* seg_of_token,
                                   void* q_out, int act_dtype, const IbKvView* kv, int write_kv, int T, int heads, unsigned* status,
-                                  const float* bias, int qk_dim, int v_dim, cudaStream_t stream) {
+                                  const float* bias, int qk_dim, int v_dim, int row, int q_col, int k_col, int v_col, int unit_norm_after, cudaStream_t stream) {
   // qk_dim, v_dim: 0 = the cache's row size. bias: float32, one value per column of the projection, or null.
+  // row, q_col, k_col, v_col, unit_norm_after: see the kernel; row = 0 stands for the row [q | k | v] alone.
   if (T == 0) return 0;
   if (check_view("qk_norm_rope_kv", kv, heads)) return 1;
   if (qk_dim <= 0) qk_dim = kv->head_dim;
@@ -303,7 +329,9 @@ extern "C" int ib_qk_norm_rope_kv(const float* qkv, int P, long long stride_p, c
   unsigned blocks = (unsigned)((items + kWarps - 1) / kWarps);
   const int hd = kv->head_dim;
   const bool aligned = ((uintptr_t)qkv % 16 == 0) && (stride_p % 4 == 0) && ((uintptr_t)q_out % 16 == 0) && ((uintptr_t)kv->base % 16 == 0);
-  const bool vec = (hd == 64 || hd == 128) && qk_dim == hd && v_dim == hd && (rot_half == 0 || 2 * rot_half == hd) && aligned;
+  IB_CHECK_ARG(row == 0 || (q_col >= 0 && k_col >= 0 && q_col + heads * qk_dim <= row && k_col + kv->kv_heads * qk_dim <= row && (v_col < 0 ? v_dim == qk_dim : v_col + kv->kv_heads * v_dim <= row)),
+               "qk_norm_rope_kv: the parts at %d, %d, %d do not fit a row of %d (values that are the keys need the keys' size)", q_col, k_col, v_col, row);
+  const bool vec = row == 0 && !unit_norm_after && (hd == 64 || hd == 128) && qk_dim == hd && v_dim == hd && (rot_half == 0 || 2 * rot_half == hd) && aligned;
   const float* cs = rot_half ? cos_t : nullptr;
   if (vec) {
     const int slots = heads + 2 * kv->kv_heads;
@@ -330,18 +358,20 @@ extern "C" int ib_qk_norm_rope_kv(const float* qkv, int P, long long stride_p, c
   else if (act_dtype == IB_F32)
     ib::launch(qk_norm_rope_kv_kernel<float, float>, blocks, kWarps * 32, 0, stream, qkv, P, (size_t)stride_p, q_norm_w, k_norm_w, eps, cos_t, sin_t,
                                                                             rot_half, positions, seg_of_token, (float*)q_out, *kv, write_kv,
-                                                                            T, heads, status, bias, qk_dim, v_dim);
+                                                                            T, heads, status, bias, qk_dim, v_dim, row, q_col, k_col, v_col, unit_norm_after);
   else
     ib::launch(qk_norm_rope_kv_kernel<__nv_bfloat16, __nv_bfloat16>, blocks, kWarps * 32, 0, stream, 
         qkv, P, (size_t)stride_p, q_norm_w, k_norm_w, eps, cos_t, sin_t, rot_half, positions, seg_of_token, (__nv_bfloat16*)q_out, *kv,
-        write_kv, T, heads, status, bias, qk_dim, v_dim);
+        write_kv, T, heads, status, bias, qk_dim, v_dim, row, q_col, k_col, v_col, unit_norm_after);
   IB_CHECK_LAUNCH("qk_norm_rope_kv");
   return 0;
 }
 
 extern "C" int ib_attention_generic(const void* q, int act_dtype, const IbKvView* kv, const int* positions, const int* seg_of_token,
                                     int window, float scale, void* out, int T, int heads, unsigned* status, int qk_dim, int v_dim, float softcap, int sink,
-                                    cudaStream_t stream) {
+                                    int chunk, const float* sink_values, const float* gate, int gate_P, long long gate_stride, int gate_row, float out_scale,
+                                    int out_row, cudaStream_t stream) {
+  // chunk, sink_values, gate, out_scale, out_row: see the kernel; out_row = 0 stands for heads * v_dim, gate = null for no gate.
   // qk_dim, v_dim: 0 = the cache's row size; softcap: 0 = scores as they are; sink: 1 = one added to the softmax's denominator.
   if (T == 0) return 0;
   if (check_view("attention_generic", kv, heads)) return 1;
@@ -350,14 +380,18 @@ extern "C" int ib_attention_generic(const void* q, int act_dtype, const IbKvView
   IB_CHECK_ARG(qk_dim <= kv->head_dim && v_dim <= kv->head_dim, "attention_generic: head sizes %d and %d exceed the cache's row of %d", qk_dim, v_dim, kv->head_dim);
   IB_CHECK_ARG((act_dtype == IB_F32 && kv->dtype == IB_F32) || (act_dtype == IB_BF16 && kv->dtype == IB_BF16),
                "attention_generic: activation dtype %d and cache dtype %d must match", act_dtype, kv->dtype);
+  if (out_row <= 0) out_row = heads * v_dim;
+  IB_CHECK_ARG(out_row >= heads * v_dim && chunk >= 0 && (!sink_values || sink), "attention_generic: bad output row %d, chunk %d or sink values without a sink", out_row, chunk);
   long long items = (long long)T * heads;
   unsigned blocks = (unsigned)((items + kWarps - 1) / kWarps);
   if (act_dtype == IB_F32)
     ib::launch(attention_generic_kernel<float, float>, blocks, kWarps * 32, 0, stream, (const float*)q, *kv, positions, seg_of_token, window, scale,
-                                                                              (float*)out, T, heads, status, qk_dim, v_dim, softcap, sink);
+                                                                              (float*)out, T, heads, status, qk_dim, v_dim, softcap, sink, chunk, sink_values, gate,
+                                                                              gate_P, (size_t)gate_stride, gate_row, out_scale, out_row);
   else
     ib::launch(attention_generic_kernel<__nv_bfloat16, __nv_bfloat16>, blocks, kWarps * 32, 0, stream, 
-        (const __nv_bfloat16*)q, *kv, positions, seg_of_token, window, scale, (__nv_bfloat16*)out, T, heads, status, qk_dim, v_dim, softcap, sink);
+        (const __nv_bfloat16*)q, *kv, positions, seg_of_token, window, scale, (__nv_bfloat16*)out, T, heads, status, qk_dim, v_dim, softcap, sink, chunk,
+        sink_values, gate, gate_P, (size_t)gate_stride, gate_row, out_scale, out_row);
   IB_CHECK_LAUNCH("attention_generic");
   return 0;
 }

@@ -28,7 +28,9 @@ __global__ void __launch_bounds__(kCols * 16) gated_recurrence_kernel(const floa
                                         const float* __restrict__ lower, float* __restrict__ state, size_t slot_stride, const int* __restrict__ seg_start,
                                         const int* __restrict__ seg_slot, float* __restrict__ o_out, int heads, int D, int V, int DS,
                                         const int* __restrict__ seg_list, const int* __restrict__ chunks, float* __restrict__ chunk_state,
-                                        float* __restrict__ chunk_decay, float* __restrict__ qa_out) {
+                                        float* __restrict__ chunk_decay, float* __restrict__ qa_out, int form, int q_col, int f_col, int v_col) {
+  // form 0: the gated form above (columns [q | f | v] at q_col, f_col, v_col of a row of R). form 1: a fixed decay per head and a key:
+  // S <- lower[a] S + k v^T with q, k, v = silu of the columns at q_col, f_col, v_col (f_bias is not read; lower holds one decay a head).
   // seg_list: the segments this launch walks (null: all). chunks != null: blockIdx.x is a chunk (first row, rows) that starts from a zero
   // state and leaves its closing state in chunk_state[chunk][head], its decay in chunk_decay[chunk][head] and q * decay in qa_out[row][head].
   extern __shared__ float sm[];   // q[kChunk][D], f[kChunk][D], g[kChunk][D], v[kChunk][kCols], running decay [D]
@@ -62,7 +64,7 @@ __global__ void __launch_bounds__(kCols * 16) gated_recurrence_kernel(const floa
     st[r][0] = (!chunks && d < D && j < V) ? S[(size_t)d * V + j] : 0.f;
     st[r][1] = (!chunks && d < D && j + 1 < V) ? S[(size_t)d * V + j + 1] : 0.f;
   }
-  const int q_off = a * D, f_off = heads * D + a * D, v_off = 2 * heads * D + a * V + j0;
+  const int q_off = q_col + a * D, f_off = f_col + a * D, v_off = v_col + a * V + j0;
   for (int c0 = t0; c0 < t1; c0 += kChunk) {
     const int n = min(kChunk, t1 - c0);
     __syncthreads();
@@ -71,13 +73,18 @@ __global__ void __launch_bounds__(kCols * 16) gated_recurrence_kernel(const floa
       const float* src = proj + (size_t)(c0 + tt) * R;
       float zq = src[q_off + d], zf = src[f_off + d];
       for (int p = 1; p < P; p++) zq += src[p * stride_p + q_off + d], zf += src[p * stride_p + f_off + d];
-      zf += f_bias[a * D + d];
-      const float lo = lower[a * D + d];
-      const float sig = 1.f / (1.f + expf(-zf));
-      const float f = __fmaf_rn(1.f - lo, sig, lo);
       sq[i] = zq / (1.f + expf(-zq));
-      sf[i] = f;
-      sg[i] = 1.f - f;
+      if (form == 1) {
+        sf[i] = lower[a];
+        sg[i] = zf / (1.f + expf(-zf));
+      } else {
+        zf += f_bias[a * D + d];
+        const float lo = lower[a * D + d];
+        const float sig = 1.f / (1.f + expf(-zf));
+        const float f = __fmaf_rn(1.f - lo, sig, lo);
+        sf[i] = f;
+        sg[i] = 1.f - f;
+      }
     }
     for (int i = tid; i < n * kCols; i += blockDim.x) {
       const int tt = i / kCols, c = i % kCols;
@@ -86,6 +93,7 @@ __global__ void __launch_bounds__(kCols * 16) gated_recurrence_kernel(const floa
         const float* src = proj + (size_t)(c0 + tt) * R + v_off + c;
         z = src[0];
         for (int p = 1; p < P; p++) z += src[p * stride_p];
+        if (form == 1) z = z / (1.f + expf(-z));
       }
       sv[i] = z;
     }
@@ -248,8 +256,11 @@ __global__ void head_rmsnorm_kernel(const float* __restrict__ o, const float* __
 // ib_recurrence_chunks_finish needs.
 extern "C" int ib_gated_recurrence(const float* proj, int P, long long stride_p, const float* f_bias, const float* lower, float* state, long long slot_stride,
                                    const int* seg_start, const int* seg_slot, int n_segments, float* o_out, int heads, int D, int V, const int* seg_list,
-                                   const int* chunks, float* chunk_state, float* chunk_decay, float* qa, cudaStream_t stream) {
+                                   const int* chunks, float* chunk_state, float* chunk_decay, float* qa, int form, int row, int q_col, int f_col, int v_col,
+                                   cudaStream_t stream) {
+  // form, row, q_col, f_col, v_col: see the kernel; row <= 0 stands for the gated form's own row [q | f | v] with its columns.
   if (n_segments == 0) return 0;
+  IB_CHECK_ARG(form == 0 || form == 1, "gated_recurrence: form %d is not known (0: gated, 1: fixed decay with a key)", form);
   IB_CHECK_ARG(!chunks || (chunk_state && chunk_decay && qa), "gated_recurrence: chunks need their state, decay and query buffers");
   IB_CHECK_ARG(n_segments > 0 && P >= 1 && heads > 0 && D > 0 && V > 0, "gated_recurrence: bad sizes segments=%d P=%d heads=%d D=%d V=%d", n_segments, P, heads, D, V);
   IB_CHECK_ARG(D <= 512, "gated_recurrence: a head's key size %d is above 512", D);
@@ -258,13 +269,17 @@ extern "C" int ib_gated_recurrence(const float* proj, int P, long long stride_p,
   int DS = 1;
   while (DS * rpt < D) DS *= 2;
   if (DS < 2) DS = 2;   // a CTA is a whole warp at least (kCols / 2 column pairs x DS)
-  const int R = 2 * heads * D + heads * V;
+  int R = 2 * heads * D + heads * V;
+  if (row <= 0) q_col = 0, f_col = heads * D, v_col = 2 * heads * D;
+  else R = row;
+  IB_CHECK_ARG(q_col >= 0 && f_col >= 0 && v_col >= 0 && q_col + heads * D <= R && f_col + heads * D <= R && v_col + heads * V <= R,
+               "gated_recurrence: the columns %d, %d, %d do not fit a row of %d", q_col, f_col, v_col, R);
   const size_t smem = ((size_t)kChunk * (3 * D + kCols) + D) * sizeof(float);
   const dim3 grid((unsigned)n_segments, (unsigned)heads, (unsigned)((V + kCols - 1) / kCols));
   auto go = [&](auto kernel) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ib::launch(kernel, grid, kCols / 2 * DS, smem, stream, proj, P, (size_t)stride_p, R, f_bias, lower, state, (size_t)slot_stride, seg_start, seg_slot, o_out, heads, D, V, DS,
-               seg_list, chunks, chunk_state, chunk_decay, qa);
+               seg_list, chunks, chunk_state, chunk_decay, qa, form, q_col, f_col, v_col);
   };
   if (rpt == 8) go(gated_recurrence_kernel<8, 32>);
   else go(gated_recurrence_kernel<16, 16>);

@@ -48,8 +48,8 @@ _SIGNATURES = {
     "ib_add_rmsnorm": [_p, _p, _i, _ll, _p, _p, _i, _p, _i, _i, _f, _i, _p],
     "ib_rope_table": [_p, _p, _p, _p, _i, _i, _p],
     "ib_silu_mul": [_p, _i, _ll, _p, _i, _i, _i, _p],
-    "ib_qk_norm_rope_kv": [_p, _i, _ll, _p, _p, _f, _p, _p, _i, _p, _p, _p, _i, C.POINTER(KvView), _i, _i, _i, _p, _p, _i, _i, _p],
-    "ib_attention_generic": [_p, _i, C.POINTER(KvView), _p, _p, _i, _f, _p, _i, _i, _p, _i, _i, _f, _i, _p],
+    "ib_qk_norm_rope_kv": [_p, _i, _ll, _p, _p, _f, _p, _p, _i, _p, _p, _p, _i, C.POINTER(KvView), _i, _i, _i, _p, _p, _i, _i, _i, _i, _i, _i, _i, _p],
+    "ib_attention_generic": [_p, _i, C.POINTER(KvView), _p, _p, _i, _f, _p, _i, _i, _p, _i, _i, _f, _i, _i, _p, _p, _i, _ll, _i, _f, _i, _p],
     "ib_gemm_simt": [_p, _i, _p, _i, _p, _i, _i, _i, _p],
     "ib_sample_rows": [_p, _i, _i, _p, _p, _p, _p, _p],
     "ib_advance_rows": [_p, _p, _p, _p, _p, _p, _p, _i, _i, _p],

@@ -166,16 +166,21 @@ def silu_mul(gate_up: torch.Tensor, act: torch.Tensor) -> None:
 def qk_norm_rope_kv(qkv: torch.Tensor, q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], eps: float,
                     cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], positions: torch.Tensor, seg_of_token: torch.Tensor,
                     q_out: torch.Tensor, kv: KvLayerView, heads: int, status: torch.Tensor, write_kv: bool = True,
-                    bias: Optional[torch.Tensor] = None, qk_dim: Optional[int] = None, v_dim: Optional[int] = None) -> None:
+                    bias: Optional[torch.Tensor] = None, qk_dim: Optional[int] = None, v_dim: Optional[int] = None,
+                    columns: Optional[tuple] = None, unit_norm_after: bool = False) -> None:
     """qkv float32 [P, T, (heads + kv_heads) * qk_dim + kv_heads * v_dim] -> q_out [T, heads * qk_dim] and the paged cache.
     qk_dim, v_dim: a query/key head's and a value head's size (default: the cache's row; neither may exceed it). bias: float32, one
-    value per column of the projection, added to the summed partial products."""
+    value per column of the projection, added to the summed partial products.
+    columns = (q, k, v): the projection's row is wider and the three parts start at these columns; v None: the values are the keys as
+    projected (bias added, no norm, no rotation). unit_norm_after: q and k are divided by their root mean square over the head after
+    the rotation, without weights."""
     _check("qkv", qkv, torch.float32)
     P, T, R = qkv.shape
     view = kv.c_view()
     qk_dim, v_dim = qk_dim or view.head_dim, v_dim or view.head_dim
-    if R != (heads + view.kv_heads) * qk_dim + view.kv_heads * v_dim:
+    if columns is None and R != (heads + view.kv_heads) * qk_dim + view.kv_heads * v_dim:
         raise L.KernelError(f"qkv has {R} columns, expected {(heads + view.kv_heads) * qk_dim + view.kv_heads * v_dim}")
+    row, q_col, k_col, v_col = (0, 0, 0, 0) if columns is None else (R, int(columns[0]), int(columns[1]), -1 if columns[2] is None else int(columns[2]))
     _check("q_out", q_out, None, (T, heads * qk_dim))
     if bias is not None:
         _check("bias", bias, torch.float32, (R,))
@@ -191,23 +196,41 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_norm_w: Optional[torch.Tensor], k_norm_
             _check(name, w, torch.float32, (view.head_dim,))
     L.call("ib_qk_norm_rope_kv", qkv.data_ptr(), P, T * R, _ptr(q_norm_w), _ptr(k_norm_w), float(eps), _ptr(cos), _ptr(sin), rot_half,
            positions.data_ptr(), seg_of_token.data_ptr(), q_out.data_ptr(), dtype_code(q_out.dtype), C.byref(view), 1 if write_kv else 0, T,
-           heads, status.data_ptr(), _ptr(bias), qk_dim, v_dim, _stream())
+           heads, status.data_ptr(), _ptr(bias), qk_dim, v_dim, row, q_col, k_col, v_col, 1 if unit_norm_after else 0, _stream())
 
 
 def attention_generic(q: torch.Tensor, kv: KvLayerView, positions: torch.Tensor, seg_of_token: torch.Tensor, window: Optional[int],
                       scale: float, out: torch.Tensor, heads: int, status: torch.Tensor, qk_dim: Optional[int] = None, v_dim: Optional[int] = None,
-                      softcap: float = 0.0, sink: bool = False) -> None:
+                      softcap: float = 0.0, sink: bool = False, chunk: int = 0, sink_values: Optional[torch.Tensor] = None,
+                      gate: Optional[tuple] = None, out_scale: float = 1.0) -> None:
     """softcap > 0: scores become softcap * tanh(score / softcap); sink: the softmax's denominator has one added (a key of score 0
-    without a value); qk_dim, v_dim: a query/key head's and a value head's size (default: the cache's row)."""
+    without a value; with sink_values, float32 [heads], a key of that score per head); qk_dim, v_dim: a query/key head's and a value
+    head's size (default: the cache's row). chunk > 0: a position sees the earlier positions of its own block of `chunk` positions
+    (counted from 0) instead of a window. gate = (float32 partial sums [P, T, row], column of the first head): head h's output is
+    multiplied by the sigmoid of its column. out_scale multiplies the output. out may be wider than heads * v_dim (a row of a larger
+    buffer whose first columns are written)."""
     view = kv.c_view()
     T = q.shape[0]
     qk_dim, v_dim = qk_dim or view.head_dim, v_dim or view.head_dim
     _check("q", q, None, (T, heads * qk_dim))
-    _check("out", out, q.dtype, (T, heads * v_dim))
+    _check("out", out, q.dtype)
+    if out.dim() != 2 or out.shape[0] != T or out.shape[1] < heads * v_dim:
+        raise L.KernelError(f"attention_generic: out must be [{T}, >= {heads * v_dim}], got {tuple(out.shape)}")
+    if sink_values is not None:
+        _check("sink_values", sink_values, torch.float32, (heads,))
+    g_ptr, g_P, g_stride, g_row = None, 0, 0, 0
+    if gate is not None:
+        g, col = gate
+        _check("gate", g, torch.float32)
+        g_P, g_row = g.shape[0], g.shape[2]
+        if g.shape[1] != T or col + heads > g_row:
+            raise L.KernelError(f"attention_generic: the gate's partial sums {tuple(g.shape)} do not hold {heads} columns from {col} for {T} tokens")
+        g_ptr, g_stride = g.data_ptr() + 4 * col, T * g_row
     _check("positions", positions, torch.int32, (T,))
     _check("seg_of_token", seg_of_token, torch.int32, (T,))
     L.call("ib_attention_generic", q.data_ptr(), dtype_code(q.dtype), C.byref(view), positions.data_ptr(), seg_of_token.data_ptr(),
-           int(window or 0), float(scale), out.data_ptr(), T, heads, status.data_ptr(), qk_dim, v_dim, float(softcap or 0.0), 1 if sink else 0, _stream())
+           int(window or 0), float(scale), out.data_ptr(), T, heads, status.data_ptr(), qk_dim, v_dim, float(softcap or 0.0), 1 if sink else 0,
+           int(chunk or 0), _ptr(sink_values), g_ptr, g_P, g_stride, g_row, float(out_scale), out.shape[1], _stream())
 
 
 def gemm_simt(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
@@ -621,7 +644,7 @@ def scale_values(v: torch.Tensor, s: float) -> None:
 
 
 # ---------------------------------------------------------------- gated linear recurrence (csrc/gated_recurrence.cu)
-L.register("ib_gated_recurrence", [L._p, L._i, L._ll, L._p, L._p, L._p, L._ll, L._p, L._p, L._i, L._p, L._i, L._i, L._i, L._p, L._p, L._p, L._p, L._p, L._p])
+L.register("ib_gated_recurrence", [L._p, L._i, L._ll, L._p, L._p, L._p, L._ll, L._p, L._p, L._i, L._p, L._i, L._i, L._i, L._p, L._p, L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._p])
 L.register("ib_recurrence_chunks_finish", [L._p, L._i, L._p, L._i, L._p, L._p, L._ll, L._p, L._p, L._p, L._p, L._i, L._i, L._i, L._p])
 L.KERNELS_PER_CALL["ib_recurrence_chunks_finish"] = 2
 RECURRENCE_CHUNK = 64   # rows of a chunk of the chunked form (csrc/gated_recurrence.cu: chunk_apply takes 64 rows a CTA)
@@ -630,41 +653,48 @@ L.register("ib_head_rmsnorm", [L._p, L._p, L._f, L._p, L._i, L._ll, L._i, L._p])
 
 def gated_recurrence(proj: torch.Tensor, f_bias: torch.Tensor, lower: torch.Tensor, state: torch.Tensor, seg_start: torch.Tensor, seg_slot: torch.Tensor,
                      n_segments: int, out: torch.Tensor, heads: int, dim: int, vdim: int, seg_list: Optional[torch.Tensor] = None,
-                     long_segs: Optional[torch.Tensor] = None, chunks: Optional[torch.Tensor] = None) -> None:
+                     long_segs: Optional[torch.Tensor] = None, chunks: Optional[torch.Tensor] = None, fixed_decay: bool = False,
+                     columns: Optional[tuple] = None) -> None:
     """proj float32 [P, T, heads * (2 dim + vdim)] = partial sums of [q | f | v]; state float32 [slots, heads, dim, vdim], advanced in place for the
     step's segments; out float32 [T, heads, vdim] = S^T q after every token.
+    fixed_decay: the other form, S <- decay_head S + k v^T with q, k, v = silu of the columns [q | k | v]; `lower` then holds one decay a head
+    (float32 [heads]) and f_bias is not read. columns = (q, k or f, v): the projection's row is wider and the parts start there.
     seg_list (int32 [n]): walk only these segments, token by token. long_segs (int32 [n, 3] of (segment, first chunk, chunks)) with chunks
     (int32 [m, 2] of (first row, rows <= RECURRENCE_CHUNK)): these segments in the chunked form instead (every chunk alone from a zero
     state, then the states carried from chunk to chunk, then each chunk's incoming state applied to its rows)."""
     _check("proj", proj, torch.float32)
     P, T, R = proj.shape
-    if R != heads * (2 * dim + vdim):
+    if columns is None and R != heads * (2 * dim + vdim):
         raise L.KernelError(f"gated_recurrence: the projection has {R} columns, expected {heads * (2 * dim + vdim)}")
-    _check("f_bias", f_bias, torch.float32, (heads * dim,))
-    _check("lower", lower, torch.float32, (heads * dim,))
+    if fixed_decay:
+        _check("lower", lower, torch.float32, (heads,))
+    else:
+        _check("f_bias", f_bias, torch.float32, (heads * dim,))
+        _check("lower", lower, torch.float32, (heads * dim,))
+    form = (1 if fixed_decay else 0, 0, 0, 0, 0) if columns is None else (1 if fixed_decay else 0, R, int(columns[0]), int(columns[1]), int(columns[2]))
     _check("state", state, torch.float32)
     if tuple(state.shape[1:]) != (heads, dim, vdim):
         raise L.KernelError(f"gated_recurrence: the state must be [slots, {heads}, {dim}, {vdim}], got {tuple(state.shape)}")
     _check("out", out, torch.float32, (T, heads, vdim))
     _check("seg_start", seg_start, torch.int32)
     _check("seg_slot", seg_slot, torch.int32)
-    common = (proj.data_ptr(), P, T * R, f_bias.data_ptr(), lower.data_ptr(), state.data_ptr(), heads * dim * vdim, seg_start.data_ptr(), seg_slot.data_ptr())
+    common = (proj.data_ptr(), P, T * R, _ptr(f_bias), lower.data_ptr(), state.data_ptr(), heads * dim * vdim, seg_start.data_ptr(), seg_slot.data_ptr())
     if long_segs is None:
         if seg_list is not None:
             _check("seg_list", seg_list, torch.int32)
             n_segments = seg_list.shape[0]
-        L.call("ib_gated_recurrence", *common, n_segments, out.data_ptr(), heads, dim, vdim, _ptr(seg_list), None, None, None, None, _stream())
+        L.call("ib_gated_recurrence", *common, n_segments, out.data_ptr(), heads, dim, vdim, _ptr(seg_list), None, None, None, None, *form, _stream())
         return
     _check("long_segs", long_segs, torch.int32)
     _check("chunks", chunks, torch.int32)
     if seg_list is not None and seg_list.shape[0]:
-        L.call("ib_gated_recurrence", *common, seg_list.shape[0], out.data_ptr(), heads, dim, vdim, seg_list.data_ptr(), None, None, None, None, _stream())
+        L.call("ib_gated_recurrence", *common, seg_list.shape[0], out.data_ptr(), heads, dim, vdim, seg_list.data_ptr(), None, None, None, None, *form, _stream())
     m = chunks.shape[0]
     chunk_state = torch.empty((m, heads, dim, vdim), dtype=torch.float32, device=proj.device)
     chunk_decay = torch.empty((m, heads, dim), dtype=torch.float32, device=proj.device)
     qa = torch.empty((T, heads, dim), dtype=torch.float32, device=proj.device)
     L.call("ib_gated_recurrence", *common, m, out.data_ptr(), heads, dim, vdim, None, chunks.data_ptr(), chunk_state.data_ptr(), chunk_decay.data_ptr(), qa.data_ptr(),
-           _stream())
+           *form, _stream())
     L.call("ib_recurrence_chunks_finish", long_segs.data_ptr(), long_segs.shape[0], chunks.data_ptr(), m, seg_slot.data_ptr(), state.data_ptr(), heads * dim * vdim,
            chunk_state.data_ptr(), chunk_decay.data_ptr(), qa.data_ptr(), out.data_ptr(), heads, dim, vdim, _stream())
 
@@ -676,3 +706,145 @@ def head_rmsnorm(o: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor
     _check("w", w, torch.float32, (V,))
     _check("out", out, None, (T, heads * V))
     L.call("ib_head_rmsnorm", o.data_ptr(), w.data_ptr(), float(eps), out.data_ptr(), dtype_code(out.dtype), T * heads, V, _stream())
+
+
+# ---------------------------------------------------------------- token shift, loop entry, gated norm, xIELU (csrc/token_shift.cu)
+L.register("ib_token_shift_rows", [L._p, L._p, L._p, L._ll, L._p, L._p, L._p, L._p, L._i, L._i, L._i, L._p])
+L.register("ib_add_rmsnorm_ext", [L._p, L._p, L._i, L._ll, L._p, L._p, L._f, L._p, L._p, L._ll, L._p, L._p, L._i, L._i, L._i, L._p])
+L.register("ib_loop_pack", [L._p, L._p, L._i, L._ll, L._p, L._p, L._p, L._i, L._i, L._i, L._p])
+L.register("ib_add_bias_rows", [L._p, L._p, L._i, L._i, L._p])
+L.register("ib_xielu_rows", [L._p, L._i, L._ll, L._p, L._p, L._i, L._i, L._i, L._p])
+L.register("ib_gated_rmsnorm", [L._p, L._p, L._f, L._p, L._i, L._ll, L._i, L._f, L._p, L._i, L._i, L._i, L._i, L._p])
+
+
+def _delta(x: torch.Tensor, delta: Optional[torch.Tensor]) -> tuple:
+    """(pointer, partial sums, stride) of float32 partial sums [P, T, H] that belong to the rows of x [T, H]."""
+    if delta is None:
+        return None, 0, 0
+    T, H = x.shape
+    _check("delta", delta, torch.float32)
+    if delta.dim() != 3 or tuple(delta.shape[1:]) != (T, H):
+        raise L.KernelError(f"delta must be [P, {T}, {H}], got {tuple(delta.shape)}")
+    return delta.data_ptr(), delta.shape[0], T * H
+
+
+def token_shift_rows(h: torch.Tensor, mix: torch.Tensor, state: torch.Tensor, seg_of_token: torch.Tensor, seg_start: torch.Tensor, seg_slot: torch.Tensor,
+                     out: torch.Tensor) -> None:
+    """out[t] = h[t] + (h[t - 1] - h[t]) * mix per channel; the row before a segment's first is state[slot] (float32 [slots, H]), which then
+    becomes the segment's last row of h. h float32 [T, H]."""
+    T, H = h.shape
+    _check("h", h, torch.float32)
+    _check("mix", mix, torch.float32, (H,))
+    _check("state", state, torch.float32)
+    _check("out", out, None, (T, H))
+    L.call("ib_token_shift_rows", h.data_ptr(), mix.data_ptr(), state.data_ptr(), state.stride(0), seg_of_token.data_ptr(), seg_start.data_ptr(), seg_slot.data_ptr(),
+           out.data_ptr(), dtype_code(out.dtype), T, H, _stream())
+
+
+def add_rmsnorm_ext(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor, eps: float, out: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                    shift: Optional[tuple] = None) -> None:
+    """x += sum_p delta[p] + bias (in place); out = w * x / sqrt(mean(x^2) + eps). shift = (mix, state, seg_slot) for a step whose row t is
+    segment t: out = h + (state[slot] - h) * mix with h the normed row, which becomes the new state."""
+    T, H = x.shape
+    _check("x", x, torch.float32)
+    _check("w", w, torch.float32, (H,))
+    _check("out", out, None, (T, H))
+    d_ptr, P, stride = _delta(x, delta)
+    if bias is not None:
+        _check("bias", bias, torch.float32, (H,))
+    mix = state = slots = None
+    if shift is not None:
+        mix, state, slots = shift
+        _check("mix", mix, torch.float32, (H,))
+        _check("state", state, torch.float32)
+        _check("seg_slot", slots, torch.int32)
+    L.call("ib_add_rmsnorm_ext", x.data_ptr(), d_ptr, P, stride, _ptr(bias), w.data_ptr(), float(eps), _ptr(mix), _ptr(state), state.stride(0) if state is not None else 0,
+           _ptr(slots), out.data_ptr(), dtype_code(out.dtype), T, H, _stream())
+
+
+def loop_pack(x: torch.Tensor, delta: Optional[torch.Tensor], x0: torch.Tensor, step: torch.Tensor, packed: torch.Tensor) -> None:
+    """packed[t] = [x[t] + sum_p delta[p][t] | x0[t]] in packed's dtype; then x[t] = step (float32 [H])."""
+    T, H = x.shape
+    _check("x", x, torch.float32)
+    _check("x0", x0, torch.float32, (T, H))
+    _check("step", step, torch.float32, (H,))
+    _check("packed", packed, None, (T, 2 * H))
+    d_ptr, P, stride = _delta(x, delta)
+    L.call("ib_loop_pack", x.data_ptr(), d_ptr, P, stride, x0.data_ptr(), step.data_ptr(), packed.data_ptr(), dtype_code(packed.dtype), T, H, _stream())
+
+
+def add_bias_rows(v: torch.Tensor, bias: torch.Tensor) -> None:
+    """v[t] += bias, float32 [T, H] in place."""
+    T, H = v.shape
+    _check("v", v, torch.float32)
+    _check("bias", bias, torch.float32, (H,))
+    L.call("ib_add_bias_rows", v.data_ptr(), bias.data_ptr(), T, H, _stream())
+
+
+def xielu_rows(z: torch.Tensor, pq: torch.Tensor, act: torch.Tensor) -> None:
+    """act = xielu(sum_p z[p]) with the two numbers pq = (p, q): z > 0: softplus(p) z^2 + z / 2; else (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2."""
+    _check("z", z, torch.float32)
+    P, T, I = z.shape
+    _check("pq", pq, torch.float32, (2,))
+    _check("act", act, None, (T, I))
+    L.call("ib_xielu_rows", z.data_ptr(), P, T * I, pq.data_ptr(), act.data_ptr(), dtype_code(act.dtype), T, I, _stream())
+
+
+def gated_rmsnorm(o: torch.Tensor, w: torch.Tensor, eps: float, gate: torch.Tensor, gate_col: int, scale: float, out: torch.Tensor, out_col: int = 0) -> None:
+    """out[t, out_col : out_col + H] = scale * w * o[t] / sqrt(mean(o[t]^2) + eps) * sigmoid(sum_p gate[p, t, gate_col : gate_col + H]); o float32 [T, H]."""
+    T, H = o.shape
+    _check("o", o, torch.float32)
+    _check("w", w, torch.float32, (H,))
+    _check("gate", gate, torch.float32)
+    _check("out", out)
+    P, Tg, R = gate.shape
+    if Tg != T or gate_col + H > R or out.dim() != 2 or out.shape[0] != T or out_col + H > out.shape[1]:
+        raise L.KernelError(f"gated_rmsnorm: gate {tuple(gate.shape)} from column {gate_col} and out {tuple(out.shape)} from column {out_col} do not hold {T} rows of {H}")
+    L.call("ib_gated_rmsnorm", o.data_ptr(), w.data_ptr(), float(eps), gate.data_ptr() + 4 * gate_col, P, T * R, R, float(scale),
+           out.data_ptr() + out.element_size() * out_col, dtype_code(out.dtype), out.shape[1], T, H, _stream())
+
+
+# ---------------------------------------------------------------- selective scan (csrc/selective_scan.cu)
+L.register("ib_conv_silu", [L._p, L._i, L._ll, L._i, L._p, L._p, L._i, L._p, L._ll, L._p, L._p, L._p, L._p, L._p, L._i, L._i, L._i, L._p])
+L.register("ib_selective_scan", [L._p, L._p, L._i, L._ll, L._p, L._i, L._ll, L._i, L._p, L._p, L._p, L._p, L._p, L._ll, L._p, L._ll, L._i, L._p, L._p, L._i, L._p, L._i,
+                                 L._i, L._i, L._i, L._p])
+
+
+def conv_silu(proj: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], conv_state: torch.Tensor, seg_of_token: torch.Tensor, seg_start: torch.Tensor,
+              seg_slot: torch.Tensor, xc: torch.Tensor, xa: Optional[torch.Tensor]) -> None:
+    """xc[t, c] = silu(bias[c] + sum_j w[j, c] u[t - taps + 1 + j, c]) with u the first `inner` columns of proj (float32 partial sums [P, T, R]) and the rows
+    before a segment's first token taken from conv_state (float32 [slots, taps - 1, inner], read only). w float32 [taps, inner]; xa: xc in another dtype."""
+    _check("proj", proj, torch.float32)
+    P, T, R = proj.shape
+    taps, inner = w.shape
+    _check("w", w, torch.float32)
+    _check("conv_state", conv_state, torch.float32)
+    _check("xc", xc, torch.float32, (T, inner))
+    if xa is not None:
+        _check("xa", xa, None, (T, inner))
+    L.call("ib_conv_silu", proj.data_ptr(), P, T * R, R, w.data_ptr(), _ptr(bias), taps, conv_state.data_ptr(), conv_state.stride(0), seg_of_token.data_ptr(),
+           seg_start.data_ptr(), seg_slot.data_ptr(), xc.data_ptr(), _ptr(xa), dtype_code(xa.dtype) if xa is not None else L.F32, T, inner, _stream())
+
+
+def selective_scan(xc: torch.Tensor, low: torch.Tensor, proj: torch.Tensor, wdt: torch.Tensor, dt_bias: torch.Tensor, A: torch.Tensor, D: torch.Tensor,
+                   state: torch.Tensor, conv_state: torch.Tensor, taps: int, seg_start: torch.Tensor, seg_slot: torch.Tensor, n_segments: int, out: torch.Tensor) -> None:
+    """The scan over every segment's tokens, from and into state (float32 [slots, inner, N]); also moves conv_state on to the segment's last taps - 1 inputs.
+    xc float32 [T, inner]; low float32 partial sums [P, T, rank + 2 N] = [dt_low | B | C]; proj float32 partial sums [P, T, >= 2 inner] = [u | z];
+    wdt float32 [inner, rank]; A float32 [inner, N] (negative rates); out [T, inner] = (y + D x) * silu(z)."""
+    T, inner = xc.shape
+    N, rank = A.shape[1], wdt.shape[1]
+    _check("xc", xc, torch.float32)
+    _check("low", low, torch.float32)
+    _check("proj", proj, torch.float32)
+    if tuple(low.shape[1:]) != (T, rank + 2 * N) or proj.shape[1] != T:
+        raise L.KernelError(f"selective_scan: low {tuple(low.shape)} must be [P, {T}, {rank + 2 * N}] and proj {tuple(proj.shape)} [P, {T}, >= {2 * inner}]")
+    _check("wdt", wdt, torch.float32, (inner, rank))
+    _check("dt_bias", dt_bias, torch.float32, (inner,))
+    _check("A", A, torch.float32, (inner, N))
+    _check("D", D, torch.float32, (inner,))
+    _check("state", state, torch.float32)
+    _check("conv_state", conv_state, torch.float32)
+    _check("out", out, None, (T, inner))
+    L.call("ib_selective_scan", xc.data_ptr(), low.data_ptr(), low.shape[0], T * low.shape[2], proj.data_ptr(), proj.shape[0], T * proj.shape[2], proj.shape[2],
+           wdt.data_ptr(), dt_bias.data_ptr(), A.data_ptr(), D.data_ptr(), state.data_ptr(), state.stride(0), conv_state.data_ptr(), conv_state.stride(0), int(taps),
+           seg_start.data_ptr(), seg_slot.data_ptr(), n_segments, out.data_ptr(), dtype_code(out.dtype), inner, N, rank, _stream())

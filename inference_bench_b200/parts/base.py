@@ -28,6 +28,8 @@ class WeightSpec:
     "norm":   per-channel scale used in float32; random 1 + U(-0.1, 0.1)
     "norm_offset": the same stored around zero (the scale is 1 + w); random U(-0.2, 0.2)
     "gate_floor": lower bounds of a forget gate, used in float32; random U(0, 0.9)
+    "unit":   per-channel mixing weights, used in float32; random U(0, 1)
+    "log_rate": logarithms of decay rates, used in float32; random log U(0.5, 8)
     "mix":    weights of an average over the n entries of the tensor's last axis, used in float32; random around 1 / n
     "table":  integer table, int32."""
     name: str
@@ -149,6 +151,18 @@ class Head(Part):
         raise NotImplementedError
 
 
+class StreamPart(Part):
+    """A part that works on the residual stream itself between two executions of the schedule (the entry of a pass over looped layers,
+    for instance). A plan names it in `stream_parts`; a schedule entry's `enter = (part, occurrence)` runs it right before that entry."""
+
+    needs_embedding = False   # True: `forward` is given the embedding's output of the step as x0
+
+    def forward(self, ctx: "StepContext", x: torch.Tensor, pending: Optional[torch.Tensor], x0: Optional[torch.Tensor], occurrence: int) -> Optional[torch.Tensor]:
+        """x: float32 residual stream [T, H] (in place); pending: a contribution not yet added to it. Returns the contribution it leaves
+        for the next norm to add (or None)."""
+        raise NotImplementedError
+
+
 class Block:
     """An arrangement of norm, mixer and feed-forward around the residual stream."""
 
@@ -178,6 +192,7 @@ POSITION_ENCODINGS: dict[str, Callable[..., PositionEncoding]] = {}
 EMBEDDINGS: dict[str, Callable[..., Embedding]] = {}
 HEADS: dict[str, Callable[..., Head]] = {}
 BLOCKS: dict[str, Callable[..., Block]] = {}
+STREAM_PARTS: dict[str, Callable[..., StreamPart]] = {}
 
 
 def _register(table: dict, what: str):
@@ -197,6 +212,7 @@ register_position_encoding = _register(POSITION_ENCODINGS, "position encoding")
 register_embedding = _register(EMBEDDINGS, "embedding")
 register_head = _register(HEADS, "head")
 register_block = _register(BLOCKS, "block arrangement")
+register_stream_part = _register(STREAM_PARTS, "stream part")
 
 
 def make(table: dict, what: str, kind: str, **params):

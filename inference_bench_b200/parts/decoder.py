@@ -32,13 +32,14 @@ class Decoder:
             self.blocks.append(base.BLOCKS[lp.block](
                 _build(base.NORMS, "norm", lp.mixer_norm), _build(base.MIXERS, "mixer", lp.mixer),
                 _build(base.NORMS, "norm", lp.feed_forward_norm), _build(base.FEED_FORWARDS, "feed-forward", lp.feed_forward), **dict(lp.block_params)))
+        self.stream_parts: list[base.StreamPart] = [_build(base.STREAM_PARTS, "stream part", sp) for sp in plan.stream_parts]
         self.final_norm: base.Norm = _build(base.NORMS, "norm", plan.final_norm)
         self.head: base.Head = _build(base.HEADS, "head", plan.head)
         self.rt = None
 
     # ------------------------------------------------------------ what the loader and the cache need
     def parts(self) -> list[base.Part]:
-        out: list[base.Part] = [self.embedding]
+        out: list[base.Part] = [self.embedding, *self.stream_parts]
         for b in self.blocks:
             out += b.parts()
         return out + [self.final_norm, self.head]
@@ -90,12 +91,16 @@ class Decoder:
         if nvtx:
             nvtx.range_pop()
         pending = None
+        # a stream part that reads the embedding's output gets a copy of its own: x is updated in place from the first block on
+        x0 = self.embedding.forward(ctx) if any(sp.needs_embedding for sp in self.stream_parts) else None
         trace = ctx.trace
         if trace is not None:
             trace.append(self._residual_rows(ctx, x, None))
         for i, e in enumerate(self.plan.schedule):
             if nvtx:
                 nvtx.range_push(f"entry {i} layer {e.layer}")
+            if e.enter is not None:
+                pending = self.stream_parts[e.enter[0]].forward(ctx, x, pending, x0, e.enter[1])
             pending = self.blocks[e.layer].forward(ctx, x, pending, ctx.caches[i] if ctx.caches else None)
             if nvtx:
                 nvtx.range_pop()

@@ -36,6 +36,7 @@ class ScheduleEntry:
     execution reads instead of writing one of its own; None means it owns a cache."""
     layer: int
     cache_of: Optional[int] = None
+    enter: Optional[tuple] = None   # (stream part, occurrence): that part of `ModelPlan.stream_parts` works on the stream right before this execution
 
 
 @dataclass(frozen=True)
@@ -50,12 +51,15 @@ class ModelPlan:
     final_norm: PartSpec
     head: PartSpec
     ignored_tensors: tuple[str, ...] = ()   # names a checkpoint may carry that the model does not read
+    stream_parts: tuple = ()                # PartSpecs of parts that work on the residual stream between executions (`ScheduleEntry.enter`)
     root: str = "model"                     # the prefix the decoder's tensors are named under; the loader probes a checkpoint for its other usual places
 
     def validate(self) -> None:
         for i, e in enumerate(self.schedule):
             if not 0 <= e.layer < len(self.layers):
                 raise ValueError(f"schedule entry {i} names layer {e.layer}, but the model has {len(self.layers)} layers")
+            if e.enter is not None and not 0 <= e.enter[0] < len(self.stream_parts):
+                raise ValueError(f"schedule entry {i} names stream part {e.enter[0]}, but the model has {len(self.stream_parts)}")
             if e.cache_of is not None:
                 if not 0 <= e.cache_of < i:
                     raise ValueError(f"schedule entry {i} reads the cache of entry {e.cache_of}, which does not run before it")

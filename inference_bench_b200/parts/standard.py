@@ -22,16 +22,18 @@ class RMSNorm(base.Norm):
     precedes it (crates/kir/tests/golden/rmsnorm_sm120.cu:19-29; no unit offset for this family,
     crates/specrt/src/weights.rs:877-880)."""
 
-    def __init__(self, name: str, size: int, eps: float, unit_offset: bool = False):
-        """unit_offset: the stored weight lies around zero and the scale is 1 + w."""
-        self.name, self.size, self.eps, self.unit_offset = name, size, eps, unit_offset
+    def __init__(self, name: str, size: int, eps: float, unit_offset: bool = False, scalar: bool = False):
+        """unit_offset: the stored weight lies around zero and the scale is 1 + w. scalar: the stored weight is one number for all
+        channels (a tensor without axes); the kernels get it as a vector of equal entries."""
+        self.name, self.size, self.eps, self.unit_offset, self.scalar = name, size, eps, unit_offset, scalar
         self.w: Optional[torch.Tensor] = None
 
     def weight_specs(self):
-        return [WeightSpec(self.name, (self.size,), role="norm_offset" if self.unit_offset else "norm")]
+        return [WeightSpec(self.name, () if self.scalar else (self.size,), role="norm_offset" if self.unit_offset else "norm")]
 
     def bind(self, weights, rt):
-        self.w = rt.vector(weights[self.name])
+        w = weights[self.name]
+        self.w = rt.vector(w.reshape(1).expand(self.size) if self.scalar else w)
         if self.unit_offset:
             self.w = self.w + 1.0   # float32, once: the kernels multiply by the scale whatever it was stored as
 
@@ -281,6 +283,35 @@ class SwiGLU(base.FeedForward):
     def forward(self, ctx, h, residual=None):
         rt = ctx.rt
         return rt.linear(rt.gate_up_act(h, self.wgu), self.wd, add_to=residual)
+
+
+@base.register_feed_forward("dense_xielu")
+class DenseXielu(base.FeedForward):
+    """down(act(up h)) with the activation xIELU, whose two numbers (p, q) are a tensor of the layer:
+    act(z) = softplus(p) z^2 + z / 2 for z > 0, (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 otherwise, in float32 on the product's
+    float32 sums."""
+
+    def __init__(self, prefix: str, hidden: int, intermediate: int, names: tuple = ("up", "down", "act")):
+        self.prefix, self.hidden, self.intermediate, self.names = prefix, hidden, intermediate, tuple(names)
+        self.wu = self.wd = self.pq = None
+
+    def weight_specs(self):
+        p, (u, d, a) = self.prefix, self.names
+        return [WeightSpec(f"{p}.{u}", (self.intermediate, self.hidden)), WeightSpec(f"{p}.{d}", (self.hidden, self.intermediate)),
+                WeightSpec(f"{p}.{a}", (2,), std=0.5)]
+
+    def bind(self, weights, rt):
+        p, (u, d, a) = self.prefix, self.names
+        self.wu, self.wd, self.pq = rt.matrix(weights[f"{p}.{u}"]), rt.matrix(weights[f"{p}.{d}"]), rt.vector(weights[f"{p}.{a}"])
+
+    adds_to_residual = True   # the down projection may add to the residual stream in its epilogue
+
+    def forward(self, ctx, h, residual=None):
+        rt = ctx.rt
+        z = rt.linear(h, self.wu)
+        act = rt.empty((h.shape[0], self.intermediate))
+        ops.xielu_rows(z, self.pq, act)
+        return rt.linear(act, self.wd, add_to=residual)
 
 
 # ------------------------------------------------------------------------------------------ embedding and head

@@ -35,6 +35,10 @@ def random_tensor(spec: WeightSpec, seed: int, device="cpu", dtype=torch.bfloat1
         t = torch.rand(spec.shape, generator=g, device=device, dtype=torch.float32) * 0.9
     elif spec.role == "mix":           # weights of an average over n inputs: around 1 / n each
         t = (0.7 + 0.6 * torch.rand(spec.shape, generator=g, device=device, dtype=torch.float32)) / max(1, spec.shape[-1])
+    elif spec.role == "unit":          # mixing weights in (0, 1)
+        t = torch.rand(spec.shape, generator=g, device=device, dtype=torch.float32)
+    elif spec.role == "log_rate":      # logarithms of decay rates between 0.5 and 8
+        t = torch.log(0.5 + 7.5 * torch.rand(spec.shape, generator=g, device=device, dtype=torch.float32))
     elif spec.role == "matrix":
         t = torch.randn(spec.shape, generator=g, device=device, dtype=torch.float32) * (spec.std if std is None else std)
     else:
