@@ -197,3 +197,46 @@ def logits(cfg, w, tokens):
     """Logits at every position of one sequence, float64 [T, vocab]."""
     x = hidden_states(cfg, w, tokens)[-1]
     return scalar_norm(x, w["final.norm"], float(cfg["norm"]["eps"])) @ d(w["head"]).T
+
+
+class PlainLulenex:
+    """A model folder (config.json, model.safetensors) read without the engine's loader."""
+
+    def __init__(self, model_dir):
+        import json
+        import struct
+        from pathlib import Path
+
+        import numpy as np
+        model_dir = Path(model_dir)
+        self.cfg = json.loads((model_dir / "config.json").read_text())
+        raw = (model_dir / "model.safetensors").read_bytes()
+        n = struct.unpack("<Q", raw[:8])[0]
+        header = json.loads(raw[8:8 + n])
+        self.w = {}
+        for name, info in header.items():
+            if name == "__metadata__":
+                continue
+            a, b = info["data_offsets"]
+            data = raw[8 + n + a:8 + n + b]
+            if info["dtype"] == "BF16":
+                bits = np.frombuffer(data, dtype="<u2").astype(np.uint32) << 16
+                t = torch.from_numpy(bits.view(np.float32).copy())
+            elif info["dtype"] == "F32":
+                t = torch.from_numpy(np.frombuffer(data, dtype="<f4").copy())
+            else:
+                raise ValueError(f"{name}: dtype {info['dtype']}")
+            self.w[name] = t.reshape(info["shape"]).to(F64)
+
+    def logits(self, tokens):
+        return logits(self.cfg, self.w, tokens)
+
+    def hidden_states(self, tokens):
+        return hidden_states(self.cfg, self.w, tokens)
+
+    def greedy(self, prompt, n):
+        toks, out = list(prompt), []
+        for _ in range(n):
+            out.append(int(self.logits(toks)[-1].argmax()))
+            toks.append(out[-1])
+        return out
