@@ -304,10 +304,10 @@ def test_keys_just_inside_and_just_outside_a_block_of_positions(tmp_path, chunk,
 
 
 def test_a_left_out_sink_and_a_far_key_show(tmp_path):
-    """A sink as large as the best score takes about half of every softmax: without it the logits differ visibly. A head whose decay is 1
+    """A sink as large as the largest score a key can reach takes a good part of every softmax: without it the logits differ visibly. A head whose decay is 1
     keeps the first token for ever: 400 tokens on (through the chunked form and through single tokens) it still counts."""
     from inference_bench_b200.engine.step import StepEntry
-    model, cfg = _one_layer(tmp_path, 1000, (1.0, 0.97), 4.0, 3.5, "s")
+    model, cfg = _one_layer(tmp_path, 1000, (1.0, 0.97), 4.0, 64.0, "s")
     plain = P.PlainLulenex(model)
     toks = traces.prompt(12, 400, 64)
     want = plain.logits(toks)
@@ -316,7 +316,7 @@ def test_a_left_out_sink_and_a_far_key_show(tmp_path):
     assert ((P.logits(plain.cfg, no_sink, toks) - want).abs().amax(dim=1) / want.abs().max()).min().item() > 1e-3
     other = list(toks)
     other[0] = (toks[0] + 1) % 64
-    assert ((plain.logits(other) - want)[-8:].abs().amax(dim=1) / want.abs().max()).min().item() > 1e-3    # the first token still counts at the end
+    assert ((plain.logits(other) - want)[-8:].abs().amax(dim=1) / want.abs().max()).min().item() > 5e-4    # the first token still counts at the end
     for head in (400, 330):
         runner = _runner(model, "float32", 512, 16)
         runner.cache.admit("x")
