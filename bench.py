@@ -428,6 +428,11 @@ DESIGN_KINDS = {   # kinds of kernel by the library entry points that launch the
                 "experts": ["ib_gemm_grouped", "ib_gemm_grouped_mma", "ib_gemm_grouped_tcgen05", "ib_gemm_grouped_swiglu_tcgen05", "ib_scatter_scaled_rows"],
                 "route": ["ib_moe_route", "ib_moe_sort", "ib_moe_combine"],
                 "norm": ["ib_add_layernorm", "ib_causal_conv_rows", "ib_add_layernorm_conv_single", "ib_depth_average", "ib_qk_norm_rope_kv"], "gemm": LEAVE_OUT["gemm"]},
+    "lulenex": {"attention": ["ib_attention_generic", "ib_attention_decode_capped", "ib_attention_decode_stream_capped", "ib_attention_prefill_ws_capped"],
+                "recurrence": ["ib_gated_recurrence", "ib_recurrence_chunks_finish", "ib_gated_rmsnorm"],
+                "scan": ["ib_conv_silu", "ib_selective_scan"],
+                "norm": ["ib_add_rmsnorm", "ib_add_rmsnorm_ext", "ib_token_shift_rows", "ib_qk_norm_rope_kv", "ib_loop_pack", "ib_xielu_rows", "ib_add_bias_rows"],
+                "gemm": LEAVE_OUT["gemm"] + ["ib_gemm_xielu_tcgen05"]},
 }
 # Busadra at layer sizes that resemble small hybrid models: windowed grouped-query attention with heads of 128, a gated linear recurrence
 # whose heads hold a 128 x 128 state, and routed experts; layers in the order attention, recurrence, recurrence, attention (repeated).
@@ -476,6 +481,73 @@ def busadra_work(z: dict, layers: int, T: int, ctx: int, batch: int) -> dict:
                                "bytes": layers * 2.0 * min(batch * z["top"], z["experts"]) * 3 * z["expert_ff"] * width},
                    "norm": {"flops": 0.0, "bytes": norm_bytes(batch)}},
     }
+
+
+# Lulenex at layer sizes that resemble small hybrid models: chunked grouped-query attention with heads of 128 (blocks of 1,536 positions:
+# a prompt of 2,048 crosses one edge and a decoded token at 2,048 sees the 513 keys of its block) beside a fixed-decay recurrence whose
+# heads hold a 128 x 128 state, every fourth layer (from the third) a selective scan, dense xIELU feed-forwards; layers 1 and 2 run twice.
+# Beside it Busadra, the closest design (windowed attention and a gated recurrence of the same head sizes, two experts a token).
+LULENEX_SIZES = {
+    "small": dict(width=1024, heads=8, kv_heads=2, dim=128, chunk=1536, rec_heads=8, rec_dim=128, rec_vdim=128, inner=2048, state=16, dt_rank=64, conv=4, ff=4096, vocab=32768,
+                  experts=8, top=2, expert_ff=1408),
+    "mid": dict(width=2048, heads=16, kv_heads=4, dim=128, chunk=1536, rec_heads=16, rec_dim=128, rec_vdim=128, inner=4096, state=16, dt_rank=128, conv=4, ff=8192, vocab=32768,
+                experts=8, top=2, expert_ff=2688),
+}
+
+
+def lulenex_layer_types(layers: int) -> list:
+    return ["mamba1" if i % 4 == 2 else "parallel" for i in range(layers)]
+
+
+def lulenex_loop(layers: int):
+    return {"start": 1, "stop": 3, "times": 2} if layers >= 3 else None
+
+
+def lulenex_config(z: dict, layers: int) -> dict:
+    par = {"left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "mask": {"size": z["chunk"]}, "scale": z["dim"] ** -0.5,
+                    "rot": {"base": 1000000.0, "dims": z["dim"] // 2}}, "left_scale": 0.8,
+           "right": {"heads": z["rec_heads"], "dim": z["rec_dim"], "vdim": z["rec_vdim"], "decay": [1.0 - 0.5 ** (1 + 8 * h / z["rec_heads"]) for h in range(z["rec_heads"])]},
+           "right_scale": 0.5}
+    scan = {"inner": z["inner"], "state": z["state"], "dt_rank": z["dt_rank"], "conv": z["conv"]}
+    ls = [{"type": t, "mixer": scan if t == "mamba1" else par, "mlp": {"kind": "dense", "ff": z["ff"]}} for t in lulenex_layer_types(layers)]
+    return {"architecture": "Lulenex", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "loop": lulenex_loop(layers), "layers": ls}
+
+
+def busadra_like_lulenex(z: dict, layers: int) -> dict:
+    return busadra_config(dict(z, window=z["chunk"]), layers)
+
+
+def lulenex_runs(layers: int) -> list:
+    types, lp = lulenex_layer_types(layers), lulenex_loop(layers)
+    if lp is None:
+        return types
+    return types[:lp["start"]] + types[lp["start"]:lp["stop"]] * lp["times"] + types[lp["stop"]:]
+
+
+def lulenex_work(z: dict, layers: int, T: int, ctx: int, batch: int) -> tuple:
+    """Algorithmic FLOPs and bytes of the design's kinds of kernel for a prefill of T tokens and for a decode step of `batch` requests at
+    `ctx` tokens of context (per step, every run of a layer counted), and the matrix products' weights (elements, per step). The
+    recurrence and the scan are float32 FMAs, not tensor-core work: their floors are the bytes they must move (float32 sums of the
+    projections in, activations out and, per decoded token, the state's trip from memory and back)."""
+    runs = lulenex_runs(layers)
+    n_par, n_scan, n = runs.count("parallel"), runs.count("mamba1"), len(runs)
+    passes = lulenex_loop(layers)["times"] if lulenex_loop(layers) else 0
+    W, H, G, D, c = z["width"], z["heads"], z["kv_heads"], z["dim"], z["chunk"]
+    rh, rd, rv, I, N, R, ff = z["rec_heads"], z["rec_dim"], z["rec_vdim"], z["inner"], z["state"], z["dt_rank"], z["ff"]
+    pairs = sum(t % c + 1 for t in range(T))
+    seen = ctx % c + 1
+    rec_row = rh * (4.0 * (2 * rd + rv) + 4.0 * rv + 10.0 * rv)         # q, k, v in; o out; o and the gate in, the gated norm out
+    scan_row = I * (4.0 + 4 + 2 + 4 + 4 + 2) + 4.0 * (R + 2 * N)          # u in, x out twice; x, z in, y out; the step, B and C in
+    norm_row = n * (W * (16.0 + 6 + 14) + 6.0 * ff) + n_par * ((H + G) * D * 4.0 + 2.0 * H * D + 4.0 * G * D) + passes * W * 20.0
+    lin = n_par * ((H + G) * D + H + 2 * rh * (rd + rv) + H * D + rh * rv) * W + n_scan * (3 * I * W + (R + 2 * N) * I) + n * 2 * ff * W + passes * 2 * W * W + z["vocab"] * W
+    work = {
+        "prefill": {"attention": {"flops": n_par * 4.0 * H * D * pairs}, "recurrence": {"flops": 0.0, "bytes": n_par * T * rec_row},
+                    "scan": {"flops": 0.0, "bytes": n_scan * T * scan_row}, "norm": {"flops": 0.0, "bytes": T * norm_row}},
+        "decode": {"attention": {"flops": n_par * 4.0 * H * D * batch * seen, "bytes": n_par * 2.0 * batch * seen * G * 2 * D},
+                   "recurrence": {"flops": 0.0, "bytes": n_par * batch * (rec_row + rh * 8.0 * rd * rv)},
+                   "scan": {"flops": 0.0, "bytes": n_scan * batch * (scan_row + 8.0 * I * N)}, "norm": {"flops": 0.0, "bytes": batch * norm_row}},
+    }
+    return work, lin
 
 
 def kernel_times(engine, entries) -> dict:
@@ -569,12 +641,18 @@ def run_design(args) -> dict:
     layers = args.layers or 4
     steps, warmup = min(args.steps, 32), max(args.warmup, 3)
     out = {"design": args.design, "layers": layers, "peaks": pk_src, "sizes": {}}
-    sizes = BUSADRA_SIZES if args.design == "busadra" else DESIGN_SIZES
+    sizes = {"busadra": BUSADRA_SIZES, "lulenex": LULENEX_SIZES}.get(args.design, DESIGN_SIZES)
     for name in (args.size.split(",") if args.size else list(sizes)):
         z = sizes[name]
         report = {}
-        pair = (("busadra", busadra_config(z, layers)), ("qwen3", qwen3_like_busadra(z, layers))) if args.design == "busadra" else \
-            (("zabonex", zabonex_config(z, layers)), ("qwen3", qwen3_like(z, layers)))
+        if args.design == "lulenex":
+            zb = dict(z, window=z["chunk"])
+            pair = (("lulenex", lulenex_config(z, layers)), ("busadra", busadra_like_lulenex(z, layers)))
+        elif args.design == "busadra":
+            zb = z
+            pair = (("busadra", busadra_config(z, layers)), ("qwen3", qwen3_like_busadra(z, layers)))
+        else:
+            pair = (("zabonex", zabonex_config(z, layers)), ("qwen3", qwen3_like(z, layers)))
         for arch, cfg in pair:
             engine = Engine(cfg, dtype="bfloat16", max_ctx=CONTEXT, page_size=PAGE_ENGINE, num_pages=64 * (CONTEXT // PAGE_ENGINE) + 64, max_num_seqs=64,
                             max_batched_tokens=8192, prefill_chunk=PROMPT, random_weights_seed=0)
@@ -583,8 +661,10 @@ def run_design(args) -> dict:
                 work = design_work(z, layers, PROMPT, PROMPT, 8)
                 lin = layers * (z["heads"] * (z["dim"] + z["rot"]) + z["heads"] * z["vdim"]) * z["width"] + (layers + 1) // 2 * (z["rank"] + z["rot"]) * z["width"] + \
                     3 * z["dense_ff"] * z["width"] + (layers - 1) * (3 * z["shared_ff"] + z["experts"]) * z["width"] + vocab * z["width"]
+            elif arch == "lulenex":
+                work, lin = lulenex_work(z, layers, PROMPT, PROMPT, 8)
             elif arch == "busadra":
-                work = busadra_work(z, layers, PROMPT, PROMPT, 8)
+                work = busadra_work(zb, layers, PROMPT, PROMPT, 8)
                 n_att = sum(1 for i in range(layers) if i % 4 in (0, 3))
                 lin = n_att * (2 * z["heads"] + 2 * z["kv_heads"]) * z["dim"] * z["width"] + \
                     (layers - n_att) * z["rec_heads"] * (2 * z["rec_dim"] + 2 * z["rec_vdim"]) * z["width"] + layers * z["experts"] * z["width"] + vocab * z["width"]
@@ -653,8 +733,9 @@ def main() -> int:
     ap.add_argument("--leave-out", default="", help="with --only decode or prefill: also time the step without each of these kinds of kernel (comma separated; "
                     "a+b leaves both out): " + ", ".join(sorted(LEAVE_OUT)))
     ap.add_argument("--only", default="", choices=["", "prefill", "decode", "mixed"], help="run one part alone (for profiling); prints a short report")
-    ap.add_argument("--design", default="", choices=["", "zabonex", "busadra"], help="measure another design beside the Qwen3 shape of equal size instead of the benchmark (prints its own report)")
-    ap.add_argument("--size", default="", help="with --design: which of its sizes (comma separated; default all): " + ", ".join(DESIGN_SIZES) + " (zabonex); " + ", ".join(BUSADRA_SIZES) + " (busadra)")
+    ap.add_argument("--design", default="", choices=["", "zabonex", "busadra", "lulenex"],
+                    help="measure another design beside the closest existing one at equal size (Qwen3; for lulenex, Busadra) instead of the benchmark (prints its own report)")
+    ap.add_argument("--size", default="", help="with --design: which of its sizes (comma separated; default all): " + ", ".join(DESIGN_SIZES) + " (zabonex); " + ", ".join(BUSADRA_SIZES) + " (busadra); " + ", ".join(LULENEX_SIZES) + " (lulenex)")
     args = ap.parse_args()
     if args.design:
         print(json.dumps(run_design(args)))

@@ -29,7 +29,7 @@ constexpr int kKS = kKeysPerWarp / 16;           // 16-key MMA steps per warp
 // units of work, of about equal size, whatever its length.
 constexpr int kMinTiles = 2;
 __device__ __forceinline__ void slice_plan(int pos, int window, int max_slices, int tiles_per_slice, int& lo, int& tile_lo, int& tps) {
-  lo = window > 0 ? max(0, pos - window + 1) : 0;
+  lo = ib::first_visible(pos, window);
   if (tiles_per_slice > 0) {
     tile_lo = 0;
     tps = tiles_per_slice;
@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(kWarps * 32)
   const int kvh = blockIdx.x, item = blockIdx.y, slice = blockIdx.z;
   const int t = dec_tokens[item];
   const int pos = positions[t], seg = seg_of_token[t];
-  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int lo = ib::first_visible(pos, window);
   const int slice_keys = tiles_per_slice * kTile;
   const int k_begin = max(lo, slice * slice_keys), k_end = min(pos + 1, (slice + 1) * slice_keys);
   if (k_begin >= k_end) return;
@@ -270,8 +270,8 @@ template <int HD>
 __global__ void __launch_bounds__(kCombineThreads)
     decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, const int* __restrict__ dec_tokens,
                           const int* __restrict__ positions, int window, __nv_bfloat16* __restrict__ out, int heads, int max_slices,
-                          int tiles_per_slice, unsigned* __restrict__ status, int sink) {
-  // sink: one more term of score 0 and no value in the denominator
+                          int tiles_per_slice, unsigned* __restrict__ status, int sink, IbAttnTail tail) {
+  // sink: one more term of score 0 (or tail.sink_values[head]) and no value in the denominator; tail: factors on the output and its row length
   constexpr int DQ = HD / 4;
   constexpr int SG = kCombineThreads / DQ;
   __shared__ float4 o_red[SG][DQ];
@@ -340,13 +340,14 @@ __global__ void __launch_bounds__(kCombineThreads)
       O.z += v.z;
       O.w += v.w;
     }
-    if (sink && M > -INFINITY) Lsum += exp2f(-M);
+    if (sink && M > -INFINITY) Lsum += exp2f((tail.sink_values ? tail.sink_values[h] * 1.4426950408889634f : 0.f) - M);
     if (!(Lsum > 0.f)) {
       O = make_float4(0.f, 0.f, 0.f, 0.f);
       Lsum = 1.f;
     }
+    if (tail.gate || tail.out_scale != 0.f) Lsum /= ib::tail_factor(tail, t, h);
     uint2 packed = make_uint2(mt::pack_bf16(O.x / Lsum, O.y / Lsum), mt::pack_bf16(O.z / Lsum, O.w / Lsum));
-    *(uint2*)&out[((size_t)t * heads + h) * HD + 4 * dq] = packed;
+    *(uint2*)&out[(size_t)t * (tail.out_row ? tail.out_row : heads * HD) + h * HD + 4 * dq] = packed;
   }
 }
 
@@ -844,7 +845,8 @@ inline int stream_merge_cols(int group, int hd) {
 template <int HD, bool FUSED>
 int launch_stream(const void* q, const RawQkv* raw, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions, const int* seg_of_token,
                   int window, float scale, float* part_o, float* part_ml, void* out, int heads, int max_slices, int tiles_per_slice,
-                  const CUtensorMap* kv_map, long long view_row0, unsigned* status, cudaStream_t stream, float softcap = 0.f, int sink = 0) {
+                  const CUtensorMap* kv_map, long long view_row0, unsigned* status, cudaStream_t stream, float softcap = 0.f, int sink = 0,
+                  const IbAttnTail& tail = IbAttnTail{}) {
   const float scale_log2e = (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, cap_pre = softcap > 0.f ? scale / softcap : 0.f;
   const int group = heads / kv->kv_heads;
   const int merge_cols = stream_merge_cols(group, HD);
@@ -870,7 +872,7 @@ int launch_stream(const void* q, const RawQkv* raw, const IbKvView* kv, const in
              *kv_map, view_row0, ib_wait_limit_ns(), status, cap_pre);
   IB_CHECK_LAUNCH("attention_decode_stream split");
   ib::launch(decode_combine_kernel<HD>, dim3(heads, n_dec), kCombineThreads, 0, stream, part_o, part_ml, dec_tokens, positions, window, (__nv_bfloat16*)out, heads,
-             max_slices, tiles_per_slice, status, sink);
+             max_slices, tiles_per_slice, status, sink, tail);
   IB_CHECK_LAUNCH("attention_decode_stream combine");
   return 0;
 }
@@ -878,7 +880,7 @@ int launch_stream(const void* q, const RawQkv* raw, const IbKvView* kv, const in
 template <int HD>
 int launch(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions, const int* seg_of_token, int window,
            float scale, float* part_o, float* part_ml, void* out, int heads, int max_slices, int tiles_per_slice, unsigned* status,
-           cudaStream_t stream, float softcap = 0.f, int sink = 0) {
+           cudaStream_t stream, float softcap = 0.f, int sink = 0, const IbAttnTail& tail = IbAttnTail{}) {
   const float scale_log2e = (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, cap_pre = softcap > 0.f ? scale / softcap : 0.f;
   constexpr int smem = 16 * HD * 2 + 4 * kTile * HD * 2 + 2 * kTile * 8;   // Q, two stages of K and V, key offsets
   static_assert(kWarps * 16 * HD * 4 <= 4 * kTile * HD * 2, "the merge buffer must fit in the tiles");
@@ -893,7 +895,7 @@ int launch(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, 
              scale_log2e, part_o, part_ml, heads, max_slices, tiles_per_slice, status, cap_pre);
   IB_CHECK_LAUNCH("attention_decode split");
   ib::launch(decode_combine_kernel<HD>, dim3(heads, n_dec), kCombineThreads, 0, stream, part_o, part_ml, dec_tokens, positions, window, (__nv_bfloat16*)out, heads,
-             max_slices, tiles_per_slice, status, sink);
+             max_slices, tiles_per_slice, status, sink, tail);
   IB_CHECK_LAUNCH("attention_decode combine");
   return 0;
 }
@@ -929,11 +931,29 @@ extern "C" int ib_make_kv_map(void* map_out, const void* pool_base, long long to
   return 0;
 }
 
-// softcap > 0: scores become softcap * tanh(score / softcap) after the scale; sink: the softmax's denominator has one added.
+namespace {
+// The tail as the kernels take it (null: all zero), or false with the error set.
+bool read_tail(const char* who, const IbAttnTail* in, int sink, int heads, const IbKvView* kv, IbAttnTail& tail) {
+  tail = in ? *in : IbAttnTail{};
+  if ((!tail.sink_values || sink) && (tail.out_row == 0 || (kv && tail.out_row >= heads * kv->head_dim && tail.out_row % 4 == 0)) &&
+      (!tail.gate || (tail.gate_parts >= 1 && tail.gate_row >= heads)))
+    return true;
+  ib_set_error("%s: sink scores without a sink, an output row of %d (a multiple of 4 that holds the heads), or a gate of %d parts and rows of %d", who, tail.out_row,
+               tail.gate_parts, tail.gate_row);
+  return false;
+}
+}  // namespace
+
+// softcap > 0: scores become softcap * tanh(score / softcap) after the scale; sink: the softmax's denominator has one added (or
+// exp(tail->sink_values[head])). window < 0: a position sees the earlier positions of its own block of -window positions. tail (may be
+// null): the sink's scores, a gate and a constant on the output, the output's row length (IbAttnTail).
 extern "C" int ib_attention_decode_capped(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions,
                                           const int* seg_of_token, int window, float scale, float* part_o, float* part_ml, void* out, int heads,
-                                          int max_slices, int tiles_per_slice, float softcap, int sink, unsigned* status, cudaStream_t stream) {
+                                          int max_slices, int tiles_per_slice, float softcap, int sink, const IbAttnTail* tail_in, unsigned* status,
+                                          cudaStream_t stream) {
   if (n_dec == 0) return 0;
+  IbAttnTail tail;
+  if (!read_tail("attention_decode", tail_in, sink, heads, kv, tail)) return 1;
   IB_CHECK_ARG(kv && kv->base && kv->block_table, "attention_decode: the cache view has a null pointer");
   IB_CHECK_ARG(tiles_per_slice >= 1 && tiles_per_slice <= 1024, "attention_decode: %d tiles per slice", tiles_per_slice);
   IB_CHECK_ARG(kv->dtype == IB_BF16, "attention_decode: the cache must be bfloat16");
@@ -942,10 +962,10 @@ extern "C" int ib_attention_decode_capped(const void* q, const IbKvView* kv, con
   IB_CHECK_ARG(n_dec > 0 && n_dec <= 65535 && max_slices > 0 && max_slices <= 65535, "attention_decode: bad sizes n=%d slices=%d", n_dec, max_slices);
   if (kv->head_dim == 128)
     return launch<128>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, tiles_per_slice,
-                       status, stream, softcap, sink);
+                       status, stream, softcap, sink, tail);
   if (kv->head_dim == 64)
     return launch<64>(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, tiles_per_slice,
-                      status, stream, softcap, sink);
+                      status, stream, softcap, sink, tail);
   return ib_set_error("attention_decode: head_dim %d has no tensor-core kernel (64 and 128 have)", kv->head_dim);
 }
 
@@ -953,14 +973,17 @@ extern "C" int ib_attention_decode(const void* q, const IbKvView* kv, const int*
                                    const int* seg_of_token, int window, float scale, float* part_o, float* part_ml, void* out, int heads,
                                    int max_slices, int tiles_per_slice, unsigned* status, cudaStream_t stream) {
   return ib_attention_decode_capped(q, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices, tiles_per_slice, 0.f, 0,
-                                    status, stream);
+                                    nullptr, status, stream);
 }
 
 namespace {
 int stream_entry(const void* q, const RawQkv* raw, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions, const int* seg_of_token,
                  int window, float scale, float* part_o, float* part_ml, void* out, int heads, int max_slices, int tiles_per_slice,
-                 const void* kv_map, long long view_row0, unsigned* status, cudaStream_t stream, float softcap = 0.f, int sink = 0) {
+                 const void* kv_map, long long view_row0, unsigned* status, cudaStream_t stream, float softcap = 0.f, int sink = 0,
+                 const IbAttnTail* tail_in = nullptr) {
   if (n_dec == 0) return 0;
+  IbAttnTail tail;
+  if (!read_tail("attention_decode_stream", tail_in, sink, heads, kv, tail)) return 1;
   IB_CHECK_ARG(kv && kv->base && kv->block_table && kv_map, "attention_decode_stream: the cache view or the tensor map is a null pointer");
   IB_CHECK_ARG(kv->page_size % 8 == 0 && (kTile % kv->page_size == 0 || kv->page_size % kTile == 0),
                "attention_decode_stream: page size %d is not a multiple of 8 that divides %d or a multiple of %d", kv->page_size, kTile, kTile);
@@ -973,15 +996,15 @@ int stream_entry(const void* q, const RawQkv* raw, const IbKvView* kv, const int
   const CUtensorMap* map = (const CUtensorMap*)kv_map;
   if (kv->head_dim == 128) {
     if (raw) return launch_stream<128, true>(q, raw, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices,
-                                             tiles_per_slice, map, view_row0, status, stream, softcap, sink);
+                                             tiles_per_slice, map, view_row0, status, stream, softcap, sink, tail);
     return launch_stream<128, false>(q, raw, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices,
-                                     tiles_per_slice, map, view_row0, status, stream, softcap, sink);
+                                     tiles_per_slice, map, view_row0, status, stream, softcap, sink, tail);
   }
   if (kv->head_dim == 64) {
     if (raw) return launch_stream<64, true>(q, raw, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices,
-                                            tiles_per_slice, map, view_row0, status, stream, softcap, sink);
+                                            tiles_per_slice, map, view_row0, status, stream, softcap, sink, tail);
     return launch_stream<64, false>(q, raw, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices,
-                                    tiles_per_slice, map, view_row0, status, stream, softcap, sink);
+                                    tiles_per_slice, map, view_row0, status, stream, softcap, sink, tail);
   }
   return ib_set_error("attention_decode_stream: head_dim %d has no tensor-core kernel (64 and 128 have)", kv->head_dim);
 }
@@ -999,14 +1022,15 @@ extern "C" int ib_attention_decode_stream(const void* q, const IbKvView* kv, con
                       tiles_per_slice, kv_map, view_row0, status, stream);
 }
 
-// The same with capped scores (softcap > 0: softcap * tanh(score / softcap)) and, with sink, one added to the softmax's denominator.
+// The same with capped scores (softcap > 0: softcap * tanh(score / softcap)) and, with sink, one added to the softmax's denominator;
+// window < 0 and tail as for ib_attention_decode_capped.
 extern "C" int ib_attention_decode_stream_capped(const void* q, const IbKvView* kv, const int* dec_tokens, int n_dec, const int* positions,
                                                  const int* seg_of_token, int window, float scale, float* part_o, float* part_ml, void* out,
                                                  int heads, int max_slices, int tiles_per_slice, const void* kv_map, long long view_row0,
-                                                 float softcap, int sink, unsigned* status, cudaStream_t stream) {
+                                                 float softcap, int sink, const IbAttnTail* tail, unsigned* status, cudaStream_t stream) {
   IB_CHECK_ARG(q || n_dec == 0, "attention_decode_stream: q is a null pointer");
   return stream_entry(q, nullptr, kv, dec_tokens, n_dec, positions, seg_of_token, window, scale, part_o, part_ml, out, heads, max_slices,
-                      tiles_per_slice, kv_map, view_row0, status, stream, softcap, sink);
+                      tiles_per_slice, kv_map, view_row0, status, stream, softcap, sink, tail);
 }
 
 // The same from the output of the q/k/v projection (float32 partial sums qkv [P][T][(heads + 2 kv_heads) * head_dim],

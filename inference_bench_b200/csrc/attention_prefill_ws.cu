@@ -86,9 +86,9 @@ __global__ void __launch_bounds__(kThreads, 2)
     prefill_ws_kernel(const __nv_bfloat16* __restrict__ q, IbKvView kv, const int* __restrict__ tile_seg, const int* __restrict__ tile_row0,
                       const int* __restrict__ seg_start, const int* __restrict__ seg_pos0, int window, float scale_log2e,
                       __nv_bfloat16* __restrict__ out, int heads, const __grid_constant__ CUtensorMap kv_map, long long view_row0,
-                      unsigned long long wait_ns, unsigned* __restrict__ status, float cap_pre, int sink) {
+                      unsigned long long wait_ns, unsigned* __restrict__ status, float cap_pre, int sink, IbAttnTail tail) {
   // cap_pre != 0: a raw product s counts as tanh(s * cap_pre) (scale_log2e is then cap * log2 e); sink: the softmax has one more term
-  // of score 0 that carries no value
+  // of score 0 (or tail.sink_values[head]) that carries no value; window < 0: blocks of -window positions (ib::first_visible)
   using SM = Smem<HD>;
   constexpr int CPR = HD / 8, HB = HD / 64;
   constexpr int kTmemCols = 256;            // S0 [0,64) | S1 [64,128) | O [128, 128+HD); P_j lies over the first 32 columns of S_j
@@ -136,7 +136,8 @@ __global__ void __launch_bounds__(kThreads, 2)
   const int t0 = seg_start[seg] + row0;
   const int pos_first = seg_pos0[seg] + row0, pos_last = pos_first + rows - 1;
   const int kvh = h / (heads / kv.kv_heads);
-  const int key_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+  const int key_lo = ib::first_visible(pos_first, window);   // of the tile's rows, the first sees the earliest key
+  const int lo_last = ib::first_visible(pos_last, window);   // a tile of keys from here on is seen by every row whose position has come
   const int kt_begin = key_lo / BN, kt_end = pos_last / BN + 1;
   const int n_kt = kt_end - kt_begin;
   // a wait that ran out: say so once, and from then on nobody waits (the results are void, the status says so)
@@ -251,6 +252,7 @@ __global__ void __launch_bounds__(kThreads, 2)
     const int row = tid;
     const uint32_t t_lane = tmem + ((uint32_t)(warp * 32) << 16);
     const int my_pos = pos_first + row;
+    const int my_lo = ib::first_visible(my_pos, window);
     ib::pdl_wait();   // q comes from the kernel before
     for (int idx = tid; idx < BM * CPR; idx += kSoftmaxWarps * 32) {
       const int r = idx / CPR, cc = idx % CPR;
@@ -280,12 +282,12 @@ __global__ void __launch_bounds__(kThreads, 2)
         for (int c = 0; c < BN; c++) sr[c] = __float_as_uint(ib::tanh_fast(__uint_as_float(sr[c]) * cap_pre));
       }
       const int key0 = kt * BN;
-      const bool need_mask = key0 + BN - 1 > pos_first || key0 < key_lo || (window > 0 && key0 <= pos_last - window);
+      const bool need_mask = key0 + BN - 1 > pos_first || key0 < lo_last;
       if (need_mask) {
 #pragma unroll
         for (int c = 0; c < BN; c++) {
           const int key = key0 + c;
-          const bool live = key <= my_pos && key >= key_lo && (window <= 0 || key > my_pos - window);
+          const bool live = key <= my_pos && key >= my_lo;
           if (!live) sr[c] = 0xff800000u;  // -inf
         }
       }
@@ -351,9 +353,11 @@ __global__ void __launch_bounds__(kThreads, 2)
     wait(&v_empty[(n_kt - 1) % VS], ((n_kt - 1) / VS) & 1);
     sm100::tc_fence_after();
     if (!*gave_up) {
-      if (sink) l += ex2(-m_ref);   // the sink's weight in the units of the running sum (a row that saw no key: infinite, the output is zero)
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = out + ((size_t)(t0 + row) * heads + h) * HD;
+      // the sink's weight in the units of the running sum (a row that saw no key: infinite, the output is zero)
+      if (sink) l += ex2((tail.sink_values ? tail.sink_values[h] * 1.4426950408889634f : 0.f) - m_ref);
+      float inv = l > 0.f ? 1.f / l : 0.f;
+      if (row < rows) inv *= ib::tail_factor(tail, t0 + row, h);
+      __nv_bfloat16* dst = out + (size_t)(t0 + row) * (tail.out_row ? tail.out_row : heads * HD) + h * HD;
 #pragma unroll 1
       for (int c0 = 0; c0 < HD; c0 += 32) {
         uint32_t o[32];
@@ -385,7 +389,7 @@ __global__ void __launch_bounds__(kThreads, 2)
 template <int HD>
 int launch(const void* q, const IbKvView* kv, const int* tile_seg, const int* tile_row0, int n_tiles, const int* seg_start, const int* seg_pos0,
            int window, float scale, void* out, int heads, const CUtensorMap* kv_map, long long view_row0, unsigned* status, cudaStream_t stream,
-           float softcap, int sink) {
+           float softcap, int sink, const IbAttnTail& tail) {
   const float scale_log2e = (softcap > 0.f ? softcap : scale) * 1.4426950408889634f, cap_pre = softcap > 0.f ? scale / softcap : 0.f;
   static bool configured = false;
   if (!configured) {
@@ -394,7 +398,7 @@ int launch(const void* q, const IbKvView* kv, const int* tile_seg, const int* ti
     configured = true;
   }
   ib::launch(prefill_ws_kernel<HD>, dim3(heads, n_tiles), kThreads, Smem<HD>::kBytes, stream, (const __nv_bfloat16*)q, *kv, tile_seg, tile_row0,
-             seg_start, seg_pos0, window, scale_log2e, (__nv_bfloat16*)out, heads, *kv_map, view_row0, ib_wait_limit_ns(), status, cap_pre, sink);
+             seg_start, seg_pos0, window, scale_log2e, (__nv_bfloat16*)out, heads, *kv_map, view_row0, ib_wait_limit_ns(), status, cap_pre, sink, tail);
   IB_CHECK_LAUNCH("attention_prefill_ws");
   return 0;
 }
@@ -404,11 +408,19 @@ int launch(const void* q, const IbKvView* kv, const int* tile_seg, const int* ti
 // Attention for query tiles of 128 rows: tile i covers rows tile_row0[i].. of segment tile_seg[i]; list the
 // tiles that see the most keys first. kv_map: the tensor map of the view's pool (ib_make_kv_map), view_row0
 // the pool row where this view's keys of page 0, head 0 start.
-// softcap > 0: scores become softcap * tanh(score / softcap) after the scale; sink: the softmax's denominator has one added.
+// softcap > 0: scores become softcap * tanh(score / softcap) after the scale; sink: the softmax's denominator has one added (or
+// exp(tail->sink_values[head])). window < 0: a position sees the earlier positions of its own block of -window positions. tail (may be
+// null): the sink's scores, a gate and a constant on the output, the output's row length (IbAttnTail).
 extern "C" int ib_attention_prefill_ws_capped(const void* q, const IbKvView* kv, const int* tile_seg, const int* tile_row0, int n_tiles,
                                               const int* seg_start, const int* seg_pos0, int window, float scale, void* out, int heads,
-                                              const void* kv_map, long long view_row0, float softcap, int sink, unsigned* status, cudaStream_t stream) {
+                                              const void* kv_map, long long view_row0, float softcap, int sink, const IbAttnTail* tail_in,
+                                              unsigned* status, cudaStream_t stream) {
   if (n_tiles == 0) return 0;
+  const IbAttnTail tail = tail_in ? *tail_in : IbAttnTail{};
+  IB_CHECK_ARG((!tail.sink_values || sink) && (tail.out_row == 0 || (tail.out_row >= heads * (kv ? kv->head_dim : 0) && tail.out_row % 8 == 0)) &&
+                   (!tail.gate || (tail.gate_parts >= 1 && tail.gate_row >= heads)),
+               "attention_prefill_ws: sink scores without a sink, an output row of %d (a multiple of 8 that holds the heads), or a gate of %d parts and rows of %d",
+               tail.out_row, tail.gate_parts, tail.gate_row);
   IB_CHECK_ARG(kv && kv->base && kv->block_table && kv_map, "attention_prefill_ws: the cache view or the tensor map is a null pointer");
   IB_CHECK_ARG(kv->dtype == IB_BF16, "attention_prefill_ws: the cache must be bfloat16");
   IB_CHECK_ARG(kv->page_size % 8 == 0 && (BN % kv->page_size == 0 || kv->page_size % BN == 0),
@@ -419,16 +431,16 @@ extern "C" int ib_attention_prefill_ws_capped(const void* q, const IbKvView* kv,
   IB_CHECK_ARG(kv->page_stride % kv->head_dim == 0 && kv->v_offset % kv->head_dim == 0, "attention_prefill_ws: strides are not whole rows");
   if (kv->head_dim == 128)
     return launch<128>(q, kv, tile_seg, tile_row0, n_tiles, seg_start, seg_pos0, window, scale, out, heads, (const CUtensorMap*)kv_map, view_row0,
-                       status, stream, softcap, sink);
+                       status, stream, softcap, sink, tail);
   if (kv->head_dim == 64)
     return launch<64>(q, kv, tile_seg, tile_row0, n_tiles, seg_start, seg_pos0, window, scale, out, heads, (const CUtensorMap*)kv_map, view_row0,
-                      status, stream, softcap, sink);
+                      status, stream, softcap, sink, tail);
   return ib_set_error("attention_prefill_ws: head_dim %d has no tensor-core kernel (64 and 128 have)", kv->head_dim);
 }
 
 extern "C" int ib_attention_prefill_ws(const void* q, const IbKvView* kv, const int* tile_seg, const int* tile_row0, int n_tiles,
                                        const int* seg_start, const int* seg_pos0, int window, float scale, void* out, int heads,
                                        const void* kv_map, long long view_row0, unsigned* status, cudaStream_t stream) {
-  return ib_attention_prefill_ws_capped(q, kv, tile_seg, tile_row0, n_tiles, seg_start, seg_pos0, window, scale, out, heads, kv_map, view_row0, 0.f, 0, status,
-                                        stream);
+  return ib_attention_prefill_ws_capped(q, kv, tile_seg, tile_row0, n_tiles, seg_start, seg_pos0, window, scale, out, heads, kv_map, view_row0, 0.f, 0, nullptr,
+                                        status, stream);
 }

@@ -23,7 +23,38 @@ struct IbKvView {
   int dtype;  // IB_F32 or IB_BF16
 };
 
+// What the tensor-core attention kernels do to a head's finished sum, beyond the plain softmax: the score of the sink (an extra term of
+// the denominator without a value) per head, a gate per (token, head) and a constant on the output, and the output's row length when
+// the heads are the first columns of a wider buffer. All zero: a sink of score 0, no gate, factor 1, rows of heads * head_dim.
+struct IbAttnTail {
+  const float* sink_values;  // float32 [heads], in natural units (not scaled), or null
+  const float* gate;         // float32 partial sums [gate_parts][tokens][gate_row], offset to the first head's column, or null:
+  int gate_parts;            //   head h's output is multiplied by sigmoid(sum over the parts of gate[t][h])
+  int gate_row;
+  long long gate_stride;     // elements between consecutive parts
+  float out_scale;           // 0 stands for 1
+  int out_row;               // elements per output row; 0 stands for heads * head_dim
+};
+
 namespace ib {
+
+// The first position that `pos` sees. window > 0: itself and the window - 1 before it; window < 0: the earlier positions of its own
+// block of -window positions, blocks counted from position 0; 0: every earlier position.
+__device__ __forceinline__ int first_visible(int pos, int window) {
+  return window > 0 ? max(0, pos - window + 1) : window < 0 ? pos - pos % (-window) : 0;
+}
+
+// The factor on head h's output for token t: out_scale * sigmoid(gate).
+__device__ __forceinline__ float tail_factor(const IbAttnTail& tail, int t, int h) {
+  float f = tail.out_scale != 0.f ? tail.out_scale : 1.f;
+  if (tail.gate) {
+    const float* g = tail.gate + (size_t)t * tail.gate_row + h;
+    float z = g[0];
+    for (int p = 1; p < tail.gate_parts; p++) z += g[(size_t)p * tail.gate_stride];
+    f *= 1.f / (1.f + __expf(-z));
+  }
+  return f;
+}
 
 // Element offset of (position, kv head) in a view, or -1 when the table has no valid page there.
 __device__ __forceinline__ long long kv_offset(const IbKvView& kv, int seg, int pos, int head) {

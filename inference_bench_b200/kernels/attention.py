@@ -56,10 +56,13 @@ L.register("ib_attention_decode_fused", [L._p, L._i, L._ll, L._p, L._p, L._f, L.
 L.register("ib_attention_prefill_tc", [L._p, C.POINTER(L.KvView), L._p, L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._i, L._p, L._p])
 L.register("ib_attention_prefill_ws", [L._p, C.POINTER(L.KvView), L._p, L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._i, L._p, L._ll, L._p, L._p])
 # the same with capped scores and a sink (softcap, sink before the status word)
-L.register("ib_attention_decode_capped", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._f, L._i, L._p, L._p])
+# (softcap, sink, the output's tail or null, then the status word)
+L.register("ib_attention_decode_capped", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._f, L._i, C.POINTER(L.AttnTail),
+                                          L._p, L._p])
 L.register("ib_attention_decode_stream_capped", [L._p, C.POINTER(L.KvView), L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._ll, L._f, L._i,
-                                                 L._p, L._p])
-L.register("ib_attention_prefill_ws_capped", [L._p, C.POINTER(L.KvView), L._p, L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._i, L._p, L._ll, L._f, L._i, L._p, L._p])
+                                                 C.POINTER(L.AttnTail), L._p, L._p])
+L.register("ib_attention_prefill_ws_capped", [L._p, C.POINTER(L.KvView), L._p, L._p, L._i, L._p, L._p, L._i, L._f, L._p, L._i, L._p, L._ll, L._f, L._i, C.POINTER(L.AttnTail),
+                                              L._p, L._p])
 L.KERNELS_PER_CALL["ib_attention_decode_capped"] = 2
 L.KERNELS_PER_CALL["ib_attention_decode_stream_capped"] = 2
 
@@ -168,22 +171,49 @@ def decode_fused(ctx, qkv: torch.Tensor, q_norm_w, k_norm_w, eps: float, cos, si
 
 
 def paged_attention(ctx, q: torch.Tensor, cache: ops.KvLayerView, heads: int, window: Optional[int], scale: float, qk_dim: Optional[int] = None,
-                    v_dim: Optional[int] = None, softcap: float = 0.0, sink: bool = False) -> torch.Tensor:
+                    v_dim: Optional[int] = None, softcap: float = 0.0, sink: bool = False, chunk: int = 0, sink_values: Optional[torch.Tensor] = None,
+                    gate: Optional[tuple] = None, out_scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q [T, heads * qk_dim] (activation dtype) -> attention output [T, heads * v_dim] of the same dtype. qk_dim, v_dim: the head sizes
-    (default: the cache's row); softcap > 0 caps the scores with a tanh; sink adds one to the softmax's denominator."""
+    (default: the cache's row); softcap > 0 caps the scores with a tanh; sink adds one to the softmax's denominator, or with sink_values
+    (float32 [heads]) exp of the head's value. chunk > 0: instead of a window, a position sees the earlier positions of its own block of
+    `chunk` positions, blocks counted from position 0. gate = (float32 partial sums [P, T, row], the first head's column): head h's
+    output is multiplied by the sigmoid of its column; out_scale multiplies the output. out: a buffer [T, >= heads * v_dim] whose first
+    columns are written, instead of a new one."""
     rt = ctx.rt
     view = cache.c_view()
+    T = q.shape[0]
     qk_dim, v_dim = qk_dim or view.head_dim, v_dim or view.head_dim
-    out = rt.empty((q.shape[0], heads * v_dim), q.dtype)
-    capped = softcap > 0 or sink
+    if chunk and window:
+        raise L.KernelError("paged_attention: a window and blocks of positions exclude one another")
+    if out is None:
+        out = rt.empty((T, heads * v_dim), q.dtype)
+    elif out.dim() != 2 or out.shape[0] != T or out.shape[1] < heads * v_dim or out.dtype != q.dtype or not out.is_contiguous():
+        raise L.KernelError(f"paged_attention: out must be a contiguous [{T}, >= {heads * v_dim}] of {q.dtype}, got {tuple(out.shape)} of {out.dtype}")
+    tailed = chunk > 0 or sink_values is not None or gate is not None or out_scale != 1.0 or out.shape[1] != heads * v_dim
+    capped = softcap > 0 or sink or tailed
     generic = qk_dim != view.head_dim or v_dim != view.head_dim or not has_tensor_core_kernel(q.dtype, view.head_dim, heads, view.kv_heads)
+    generic = generic or (tailed and out.shape[1] % 8 != 0)
     work = None if generic else _work_lists(ctx)
     if capped and not generic and work["n_tiles"] and (rt.options.prefill_attention == "tcgen05" or not cache.tma()[0]):
         generic = True    # prompt portions with capped scores run on the kernel that TMA feeds, or on the generic one
     if generic:
-        ops.attention_generic(q, cache, ctx.positions, ctx.seg_of_token, window, scale, out, heads, rt.status, qk_dim, v_dim, softcap, sink)
+        ops.attention_generic(q, cache, ctx.positions, ctx.seg_of_token, window, scale, out, heads, rt.status, qk_dim, v_dim, softcap, sink, chunk=chunk,
+                              sink_values=sink_values, gate=gate, out_scale=out_scale)
         return out
-    extra = (float(softcap), 1 if sink else 0) if capped else ()
+    tail_ref = None
+    if tailed:
+        t = L.AttnTail(sink_values=ops._ptr(sink_values), gate=None, gate_parts=0, gate_row=0, gate_stride=0, out_scale=float(out_scale), out_row=out.shape[1])
+        if sink_values is not None:
+            ops._check("sink_values", sink_values, torch.float32, (heads,))
+        if gate is not None:
+            g, col = gate
+            ops._check("gate", g, torch.float32)
+            if g.dim() != 3 or g.shape[1] != T or col + heads > g.shape[2]:
+                raise L.KernelError(f"paged_attention: the gate's partial sums {tuple(g.shape)} do not hold {heads} columns from {col} for {T} tokens")
+            t.gate, t.gate_parts, t.gate_row, t.gate_stride = g.data_ptr() + 4 * col, g.shape[0], g.shape[2], T * g.shape[2]
+        tail_ref = C.byref(t)
+    window = -int(chunk) if chunk else window   # the kernels take blocks of positions as a negative window
+    extra = (float(softcap), 1 if sink else 0, tail_ref) if capped else ()
     tail = "_capped" if capped else ""
     stream = ops._stream()
     if work["n_dec"]:

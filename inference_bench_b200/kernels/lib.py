@@ -41,6 +41,19 @@ class KvView(C.Structure):
     ]
 
 
+class AttnTail(C.Structure):
+    """Mirror of IbAttnTail in csrc/kv_view.cuh."""
+    _fields_ = [
+        ("sink_values", C.c_void_p),
+        ("gate", C.c_void_p),
+        ("gate_parts", C.c_int),
+        ("gate_row", C.c_int),
+        ("gate_stride", C.c_longlong),
+        ("out_scale", C.c_float),
+        ("out_row", C.c_int),
+    ]
+
+
 _p, _i, _f, _ll = C.c_void_p, C.c_int, C.c_float, C.c_longlong
 
 _SIGNATURES = {

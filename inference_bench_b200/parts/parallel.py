@@ -11,7 +11,9 @@ Two branches exist:
 are rotated over the first `rotary_dim` entries of a head and then divided by their root mean square over the head (no weights);
 score = q.k * scale; a position sees the earlier positions of its own block of `chunk` positions, counted from the request's position
 0; the softmax's denominator also holds exp(sink_head), a learned number per head without key or value; head a's output is multiplied
-by sigmoid(W_g h)_a. Keys (rotated, normed) and values (the keys as projected) live in the paged cache.
+by sigmoid(W_g h)_a. Keys (rotated, normed) and values (the keys as projected) live in the paged cache. bfloat16 heads of 64 or 128 run on
+the tensor-core kernels (prompt portions on the flash kernel, decoded tokens on the split-context kernels: blocks of positions are their
+negative window, the sink's scores, the gate and the branch's scale their output tail); everything else on the generic kernel.
 
 "decayed_linear": per head S <- decay_head S + k v^T, o = S^T q with q, k, v = silu of their projections and S [dim, vdim] float32 state of
 the request; all heads' o are normed together (RMS norm with a weight), multiplied by sigmoid(W_g h) elementwise and projected.
@@ -96,8 +98,9 @@ class ChunkAttentionBranch:
         q_col, k_col, g_col = col0, col0 + self.heads * hd, col0 + (self.heads + self.kv_heads) * hd
         ops.qk_norm_rope_kv(proj, None, None, self.norm_eps, cos, sin, ctx.positions, ctx.seg_of_token, q, cache, self.heads, rt.status, bias=bias,
                             qk_dim=hd, v_dim=hd, columns=(q_col, k_col, None), unit_norm_after=True)
-        ops.attention_generic(q, cache, ctx.positions, ctx.seg_of_token, None, self.scale, out, self.heads, rt.status, hd, hd, sink=True, chunk=self.chunk,
-                              sink_values=self.sink, gate=(proj, g_col), out_scale=scale)
+        from ..kernels import attention
+        attention.paged_attention(ctx, q, cache, self.heads, None, self.scale, qk_dim=hd, v_dim=hd, sink=True, chunk=self.chunk, sink_values=self.sink,
+                                  gate=(proj, g_col), out_scale=scale, out=out)
 
 
 class DecayedLinearBranch:

@@ -74,6 +74,23 @@ def rotate(x, positions, dims, base):
 
 
 # ------------------------------------------------------------------------------------------ the left mixer: chunked attention with a sink
+def sink_softmax_in_blocks(q, k, v, pos, scale, size, sink):
+    """q [T, H, D], k and v [T, G, D] at positions pos -> [T, H, D]: position i weighs the positions j <= i of its own block of `size`
+    positions (i // size == j // size) by exp(q_i . k_j * scale), and the denominator also holds exp(sink) of the head."""
+    T, H, D = q.shape
+    G = k.shape[1]
+    out = torch.zeros((T, H, v.shape[2]), dtype=F64)
+    i, j = pos[:, None], pos[None, :]
+    seen = (j <= i) & (i // size == j // size)
+    for a in range(H):
+        b = a // (H // G)
+        s = ((q[:, a] @ k[:, b].T) * scale).masked_fill(~seen, -math.inf)
+        top = torch.maximum(s.max(-1, keepdim=True).values, sink[a])
+        e = torch.exp(s - top)
+        out[:, a] = (e / (e.sum(-1, keepdim=True) + torch.exp(sink[a] - top))) @ v[:, b]
+    return out
+
+
 def chunked_attention(h, w, p, m, eps):
     """Grouped-query attention whose values are its keys as projected; scores of rotated, unit-normed q and k; a position sees
     the earlier positions of its own chunk of `mask.size`; the softmax's denominator also holds exp(sink) per head; every head's
@@ -89,18 +106,7 @@ def chunked_attention(h, w, p, m, eps):
     q = rms_unit(rotate(q, pos, int(rot["dims"]), float(rot["base"])), eps)
     k = rms_unit(rotate(k, pos, int(rot["dims"]), float(rot["base"])), eps)
     gate = torch.sigmoid(h @ d(w[f"{p}.g"]).T)                      # [T, H]
-    sink = d(w[f"{p}.sink"])
-    out = torch.zeros((T, H, D), dtype=F64)
-    for a in range(H):
-        b = a // (H // G)
-        s = (q[:, a] @ k[:, b].T) * scale                            # [T, T]
-        i, j = pos[:, None], pos[None, :]
-        seen = (j <= i) & (i // size == j // size)
-        s = s.masked_fill(~seen, -math.inf)
-        top = torch.maximum(s.max(-1, keepdim=True).values, sink[a])
-        e = torch.exp(s - top)
-        den = e.sum(-1, keepdim=True) + torch.exp(sink[a] - top)
-        out[:, a] = (e / den) @ v[:, b] * gate[:, a:a + 1]
+    out = sink_softmax_in_blocks(q, k, v, pos, scale, size, d(w[f"{p}.sink"])) * gate[:, :, None]
     return out.reshape(T, H * D) @ d(w[f"{p}.o"]).T + d(w[f"{p}.o.b"])
 
 

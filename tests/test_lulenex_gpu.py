@@ -27,6 +27,12 @@ BF16_MEDIAN = 1.5e-2
 
 
 @pytest.fixture(scope="module")
+def rt16():
+    from inference_bench_b200.engine.runtime import Runtime
+    return Runtime(DEV, dtype="bfloat16")
+
+
+@pytest.fixture(scope="module")
 def ldirs(tmp_path_factory):
     root = tmp_path_factory.mktemp("lulenex")
     return {name: tl.write_model(name, root / name) for name in tl.CONFIGS}
@@ -63,6 +69,63 @@ def _walk(rt, zero_slot, step_fn):
         for r, n in step:
             at[r] += n
     assert at == LENS
+
+
+# ------------------------------------------------------------------------------------------ attention in blocks of positions with a sink, a gate and a scale
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,dim,page,block,extra", [
+    (4, 2, 64, 16, 48, 24), (8, 1, 128, 16, 100, 0), (2, 2, 128, 64, 64, 8), (6, 3, 64, 8, 130, 40), (4, 4, 64, 32, 1000, 0), (3, 1, 64, 16, 1, 5),
+    (4, 2, 32, 16, 24, 4), (5, 5, 24, 8, 13, 0), (16, 1, 64, 64, 200, 16)])
+def test_attention_in_blocks_of_positions_with_sink_gate_and_scale(rt32, rt16, dtype, heads, kv_heads, dim, page, block, extra):
+    """Prompt portions that cross edges of blocks and of pages, the first tokens of a sequence and single decoded tokens right before, at
+    and after an edge, all of one request on shuffled pages. One key stands out for one query (they share a large entry): the first key of
+    the query's block (inside) and the last of the block before (outside), a query's own position, a key far back in a long block. The
+    heads are the first columns of a wider output buffer, gated by one sigmoid a head and scaled; bfloat16 heads of 64 and 128 run on
+    the tensor-core kernels, the rest on the generic one."""
+    from inference_bench_b200.kernels import attention
+    from inference_bench_b200.kernels.ops import KvLayerView
+    rt = rt32 if dtype == torch.float32 else rt16
+    n_ctx, scale, out_scale = 420, 0.35, 0.7
+    g = torch.Generator().manual_seed(heads * dim + page + block)
+    e1 = (300 // block) * block                      # a block's first position at or below 300
+    runs = [(130, 150), (0, 7), (max(e1 - 1, 0), 1), (e1, 1), (min(e1 + 1, n_ctx - 1), 1), (410, 1), (2 * page - 2, 4), (330, 70)]
+    positions = [p0 + i for p0, n in runs for i in range(n)]
+    T = len(positions)
+    n_pages = -(-n_ctx // page)
+    perm = torch.randperm(n_pages + 3, generator=g)[:n_pages]
+    k, v = torch.randn((n_ctx, kv_heads, dim), generator=g), torch.randn((n_ctx, kv_heads, dim), generator=g)
+    q = torch.randn((n_ctx, heads, dim), generator=g) * 0.3
+    lo = lambda p: p - p % block
+    needles = [(e1, e1, 0), (e1 + 3, lo(e1 + 3), 1 % heads), (e1 + 2, lo(e1 + 2) - 1, 2 % heads), (270, lo(270), 0), (271, lo(271) - 1, 1 % heads),
+               (410, lo(410), 0), (409, 5, 1 % heads), (2 * page, 2 * page - 1, 0), (399, 331, 0)]
+    for i, (qp, key, head) in enumerate(needles):
+        if not 0 <= key < n_ctx or not 0 <= qp < n_ctx:
+            continue
+        col = (i * 5) % dim
+        k[key, head // (heads // kv_heads), col] = 5.0
+        q[qp, head, col] = 30.0
+    k, v, q = k.to(dtype).float(), v.to(dtype).float(), q.to(dtype).float()
+    sink = torch.randn((heads,), generator=g) * 2.0
+    gate_parts = torch.randn((2, T, heads + 3), generator=g)
+    pool = torch.zeros((2, n_pages + 3, 2, kv_heads, page, dim), dtype=dtype, device=DEV)
+    for j in range(n_ctx):
+        pool[1, perm[j // page], 0, :, j % page] = k[j].to(dtype)
+        pool[1, perm[j // page], 1, :, j % page] = v[j].to(dtype)
+    want = P.sink_softmax_in_blocks(q.double(), k.double(), v.double(), torch.arange(n_ctx), scale, block, sink.double())[positions]
+    want = want * torch.sigmoid(gate_parts.double().sum(0)[:, 3:])[:, :, None] * out_scale
+    ctx = _ctx(rt, runs)
+    table = perm.to(torch.int32).reshape(1, -1).repeat(len(runs), 1).contiguous().to(DEV)
+    view = KvLayerView(pool, 1, table)
+    qd = q[positions].reshape(T, heads * dim).to(DEV, dtype).contiguous()
+    out = torch.full((T, heads * dim + extra), 7.0, dtype=dtype, device=DEV)
+    attention.paged_attention(ctx, qd, view, heads, None, scale, sink=True, chunk=block, sink_values=_f32(sink), gate=(_f32(gate_parts), 3), out_scale=out_scale, out=out)
+    got = out[:, :heads * dim].float().cpu().double().view(T, heads, dim)
+    assert (out[:, heads * dim:] == 7.0).all()                     # the columns beyond the heads belong to someone else
+    tol = 3e-5 if dtype == torch.float32 else 3e-2
+    err = (got - want).abs().amax(dim=(1, 2))
+    assert err.max().item() < tol, f"positions {[positions[i] for i in torch.nonzero(err >= tol).flatten().tolist()]} differ by up to {err.max().item():.2e}"
+    rt.check_status()
+
 
 
 # ------------------------------------------------------------------------------------------ norm with one number, token shift and its state
