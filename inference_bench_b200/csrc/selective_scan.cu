@@ -12,6 +12,11 @@
 //    small product, bias and softplus; x and z), then walked in order: the exponentials sit in the walk, everything else outside it.
 //    The sum over a channel's states is a shuffle over its G lanes. After the walk the CTA writes the recurrent state and shifts the
 //    request's convolution state (it runs after every reader of the old one).
+//  * Long segments (prompt portions) are cut into chunks that are walked side by side. Since the decays of a channel's state n multiply
+//    to exp(A[c][n] * sum of the chunk's step sizes), a chunk's effect on an incoming state is S_out = exp(A sum_dt) S_in + S_local:
+//    pass 1 walks every chunk from a zero state and keeps S_local and sum_dt (no outputs), scan_chunks_carry walks a segment's chunks in
+//    order for every (c, n), leaves each chunk's incoming state where its local one was, writes the request's state and shifts its
+//    convolution state, and pass 2 walks every chunk again from its incoming state and writes the outputs.
 #include "common.cuh"
 
 namespace {
@@ -53,12 +58,33 @@ __global__ void conv_silu_kernel(const float* __restrict__ proj, int P, size_t s
   }
 }
 
+// The convolution's state of channel c becomes its inputs at the segment's last taps - 1 rows; with fewer rows than that the old state moves
+// up. Row r is written after row r + n_seg was read, and later rows read only rows further on: in place, in rising order.
+__device__ __forceinline__ void shift_conv_state(float* __restrict__ cs, const float* __restrict__ proj, int PZ, size_t z_stride, int RZ, int taps, int t0, int n_seg,
+                                                 int inner, int c) {
+  for (int r = 0; r < taps - 1; r++) {
+    const int rel = n_seg - (taps - 1) + r;
+    float v;
+    if (rel >= 0) {
+      const float* src = proj + (size_t)(t0 + rel) * RZ + c;
+      v = src[0];
+      for (int p = 1; p < PZ; p++) v += src[p * z_stride];
+    } else {
+      v = cs[(size_t)(n_seg + r) * inner + c];
+    }
+    cs[(size_t)r * inner + c] = v;
+  }
+}
+
 template <int NPT, typename O>
 __global__ void __launch_bounds__(kThreads) selective_scan_kernel(
     const float* __restrict__ xc, const float* __restrict__ low, int PL, size_t low_stride, const float* __restrict__ proj, int PZ, size_t z_stride, int RZ,
     const float* __restrict__ wdt, const float* __restrict__ dt_bias, const float* __restrict__ A, const float* __restrict__ Dv, float* __restrict__ state,
     size_t slot_stride, float* __restrict__ conv_state, size_t conv_slot_stride, int taps, const int* __restrict__ seg_start, const int* __restrict__ seg_slot,
-    O* __restrict__ out, int inner, int N, int rank, int G) {
+    O* __restrict__ out, int inner, int N, int rank, int G, const int* __restrict__ seg_list, const int* __restrict__ chunks, float* __restrict__ chunk_state,
+    float* __restrict__ chunk_dt, int pass) {
+  // pass 0: blockIdx.x is a segment (seg_list[blockIdx.x] if given), walked from and into the request's state. pass 1 and 2: blockIdx.x is
+  // a chunk (chunks[b] = (first row, rows)); chunk_state: [chunks][inner][N], chunk_dt: [chunks][inner].
   // low: [PL][T][rank + 2N] = [dt_low | B | C]; proj: [PZ][T][RZ] = [u | z] (u: the convolution's inputs, z at column `inner`);
   // wdt: float32 [inner][rank]; A: float32 [inner][N], already -exp(A_log); state: [slots][inner][N]; out: [T][inner].
   extern __shared__ float sm[];
@@ -70,19 +96,21 @@ __global__ void __launch_bounds__(kThreads) selective_scan_kernel(
   float* s_z = s_x + kStage * CH;
   ib::pdl_launch_dependents();
   ib::pdl_wait();
-  const int s = blockIdx.x, c_first = blockIdx.y * CH;
+  const int c_first = blockIdx.y * CH;
   const int tid = threadIdx.x, cl = tid / G, g = tid % G, c = c_first + cl;
-  const int t0 = seg_start[s], t1 = seg_start[s + 1];
+  const int s = pass ? 0 : (seg_list ? seg_list[blockIdx.x] : (int)blockIdx.x);
+  const int t0 = pass ? chunks[2 * blockIdx.x] : seg_start[s], t1 = pass ? t0 + chunks[2 * blockIdx.x + 1] : seg_start[s + 1];
   const bool live = c < inner;
-  float* S = state + (size_t)seg_slot[s] * slot_stride + (size_t)c * N;
+  float* S = pass ? chunk_state + ((size_t)blockIdx.x * inner + c) * N : state + (size_t)seg_slot[s] * slot_stride + (size_t)c * N;
   float st[NPT], a[NPT];
 #pragma unroll
   for (int i = 0; i < NPT; i++) {
     const int n = g + i * G;
     const bool in = live && n < N;
-    st[i] = in ? S[n] : 0.f;
+    st[i] = in && pass != 1 ? S[n] : 0.f;
     a[i] = in ? A[(size_t)c * N + n] : 0.f;
   }
+  float dt_sum = 0.f;
   for (int i = tid; i < CH * rank; i += kThreads) {
     const int cc = i / rank, r = i % rank;
     s_w[cc * WS + r] = c_first + cc < inner ? wdt[(size_t)(c_first + cc) * rank + r] : 0.f;
@@ -103,9 +131,11 @@ __global__ void __launch_bounds__(kThreads) selective_scan_kernel(
       float xv = 0.f, zv = 0.f;
       if (c_first + cc < inner) {
         xv = xc[(size_t)(b0 + tt) * inner + c_first + cc];
-        const float* src = proj + (size_t)(b0 + tt) * RZ + inner + c_first + cc;
-        zv = src[0];
-        for (int p = 1; p < PZ; p++) zv += src[p * z_stride];
+        if (pass != 1) {
+          const float* src = proj + (size_t)(b0 + tt) * RZ + inner + c_first + cc;
+          zv = src[0];
+          for (int p = 1; p < PZ; p++) zv += src[p * z_stride];
+        }
       }
       s_x[i] = xv;
       s_z[i] = zv;
@@ -123,6 +153,15 @@ __global__ void __launch_bounds__(kThreads) selective_scan_kernel(
       const float dx = dtv * xv;
       const float* bc = s_low + tt * RL + rank;
       float acc = 0.f;
+      if (pass == 1) {
+        dt_sum += dtv;
+#pragma unroll
+        for (int i = 0; i < NPT; i++) {
+          const int n = g + i * G;
+          st[i] = __fmaf_rn(expf(dtv * a[i]), st[i], dx * (n < N ? bc[n] : 0.f));
+        }
+        continue;
+      }
 #pragma unroll
       for (int i = 0; i < NPT; i++) {
         const int n = g + i * G;
@@ -137,28 +176,44 @@ __global__ void __launch_bounds__(kThreads) selective_scan_kernel(
       }
     }
   }
+  if (pass == 2) return;
 #pragma unroll
   for (int i = 0; i < NPT; i++) {
     const int n = g + i * G;
     if (live && n < N) S[n] = st[i];
   }
-  if (g == 0 && live && taps > 1) {
-    // the convolution's state becomes its inputs at the segment's last taps - 1 rows; with fewer rows than that the old state moves up.
-    // Row r is written after row r + n_seg was read, and later rows read only rows further on: in place, in rising order.
-    const int n_seg = t1 - t0;
-    float* cs = conv_state + (size_t)seg_slot[s] * conv_slot_stride;
-    for (int r = 0; r < taps - 1; r++) {
-      const int rel = n_seg - (taps - 1) + r;
-      float v;
-      if (rel >= 0) {
-        const float* src = proj + (size_t)(t0 + rel) * RZ + c;
-        v = src[0];
-        for (int p = 1; p < PZ; p++) v += src[p * z_stride];
-      } else {
-        v = cs[(size_t)(n_seg + r) * inner + c];
-      }
-      cs[(size_t)r * inner + c] = v;
+  if (pass == 1) {
+    if (g == 0 && live) chunk_dt[(size_t)blockIdx.x * inner + c] = dt_sum;
+    return;
+  }
+  if (g == 0 && live && taps > 1)
+    shift_conv_state(conv_state + (size_t)seg_slot[s] * conv_slot_stride, proj, PZ, z_stride, RZ, taps, t0, t1 - t0, inner, c);
+}
+
+__global__ void scan_chunks_carry_kernel(const int* __restrict__ long_segs, const int* __restrict__ seg_start, const int* __restrict__ seg_slot, float* __restrict__ state,
+                                         size_t slot_stride, float* __restrict__ chunk_state, const float* __restrict__ chunk_dt, const float* __restrict__ A,
+                                         const float* __restrict__ proj, int PZ, size_t z_stride, int RZ, float* __restrict__ conv_state, size_t conv_slot_stride,
+                                         int taps, int inner, int N) {
+  // long_segs: [n][3] = (segment, first chunk, chunks). One thread per (channel, state index) walks the segment's chunks in order: the
+  // chunk's local state gives way to its incoming one, and the request's state becomes the last chunk's outgoing one.
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
+  const int s = long_segs[3 * blockIdx.x], first = long_segs[3 * blockIdx.x + 1], count = long_segs[3 * blockIdx.x + 2];
+  const size_t per = (size_t)inner * N;
+  for (size_t i = (size_t)blockIdx.y * blockDim.x + threadIdx.x; i < per; i += (size_t)gridDim.y * blockDim.x) {
+    const int c = (int)(i / N);
+    float* S = state + (size_t)seg_slot[s] * slot_stride + i;
+    const float a = A[i];
+    float v = *S;
+    for (int k = first; k < first + count; k++) {
+      float* loc = chunk_state + (size_t)k * per + i;
+      const float mine = *loc;
+      *loc = v;
+      v = __fmaf_rn(expf(a * chunk_dt[(size_t)k * inner + c]), v, mine);
     }
+    *S = v;
+    if (i % N == 0 && taps > 1)
+      shift_conv_state(conv_state + (size_t)seg_slot[s] * conv_slot_stride, proj, PZ, z_stride, RZ, taps, seg_start[s], seg_start[s + 1] - seg_start[s], inner, c);
   }
 }
 
@@ -185,8 +240,10 @@ extern "C" int ib_conv_silu(const float* proj, int P, long long stride_p, int R,
 extern "C" int ib_selective_scan(const float* xc, const float* low, int PL, long long low_stride, const float* proj, int PZ, long long z_stride, int RZ, const float* wdt,
                                  const float* dt_bias, const float* A, const float* Dv, float* state, long long slot_stride, float* conv_state,
                                  long long conv_slot_stride, int taps, const int* seg_start, const int* seg_slot, int n_segments, void* out, int out_dtype, int inner,
-                                 int N, int rank, cudaStream_t stream) {
+                                 int N, int rank, const int* seg_list, const int* chunks, float* chunk_state, float* chunk_dt, int pass, cudaStream_t stream) {
+  // n_segments: the grid's first extent, that is segments (pass 0; those of seg_list if given) or chunks (pass 1 and 2).
   if (n_segments == 0) return 0;
+  IB_CHECK_ARG(pass >= 0 && pass <= 2 && (pass == 0 || (chunks && chunk_state && chunk_dt)), "selective_scan: pass %d needs the chunk table and its buffers", pass);
   IB_CHECK_ARG(n_segments > 0 && inner > 0 && N > 0 && rank > 0 && PL >= 1 && PZ >= 1 && taps >= 1, "selective_scan: bad sizes segments=%d inner=%d N=%d rank=%d", n_segments,
                inner, N, rank);
   IB_CHECK_ARG(N <= 256, "selective_scan: %d states a channel are above the 256 the kernel holds", N);
@@ -202,7 +259,7 @@ extern "C" int ib_selective_scan(const float* xc, const float* low, int PL, long
   auto go = [&](auto kernel, auto* o) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ib::launch(kernel, grid, kThreads, smem, stream, xc, low, PL, (size_t)low_stride, proj, PZ, (size_t)z_stride, RZ, wdt, dt_bias, A, Dv, state, (size_t)slot_stride,
-               conv_state, (size_t)conv_slot_stride, taps, seg_start, seg_slot, o, inner, N, rank, G);
+               conv_state, (size_t)conv_slot_stride, taps, seg_start, seg_slot, o, inner, N, rank, G, seg_list, chunks, chunk_state, chunk_dt, pass);
   };
   if (out_dtype == IB_F32) {
     if (npt == 4) go(selective_scan_kernel<4, float>, (float*)out);
@@ -214,5 +271,17 @@ extern "C" int ib_selective_scan(const float* xc, const float* low, int PL, long
     return ib_set_error("selective_scan: unknown output dtype %d", out_dtype);
   }
   IB_CHECK_LAUNCH("selective_scan");
+  return 0;
+}
+
+extern "C" int ib_scan_chunks_carry(const int* long_segs, int n_long, const int* seg_start, const int* seg_slot, float* state, long long slot_stride, float* chunk_state,
+                                    const float* chunk_dt, const float* A, const float* proj, int PZ, long long z_stride, int RZ, float* conv_state,
+                                    long long conv_slot_stride, int taps, int inner, int N, cudaStream_t stream) {
+  if (n_long == 0) return 0;
+  IB_CHECK_ARG(n_long > 0 && inner > 0 && N > 0 && taps >= 1 && PZ >= 1, "scan_chunks_carry: bad sizes segments=%d inner=%d N=%d taps=%d", n_long, inner, N, taps);
+  const dim3 grid((unsigned)n_long, (unsigned)min(((size_t)inner * N + 255) / 256, (size_t)4096));
+  ib::launch(scan_chunks_carry_kernel, grid, 256, 0, stream, long_segs, seg_start, seg_slot, state, (size_t)slot_stride, chunk_state, chunk_dt, A, proj, PZ,
+             (size_t)z_stride, RZ, conv_state, (size_t)conv_slot_stride, taps, inner, N);
+  IB_CHECK_LAUNCH("scan_chunks_carry");
   return 0;
 }

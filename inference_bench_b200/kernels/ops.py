@@ -807,7 +807,8 @@ def gated_rmsnorm(o: torch.Tensor, w: torch.Tensor, eps: float, gate: torch.Tens
 # ---------------------------------------------------------------- selective scan (csrc/selective_scan.cu)
 L.register("ib_conv_silu", [L._p, L._i, L._ll, L._i, L._p, L._p, L._i, L._p, L._ll, L._p, L._p, L._p, L._p, L._p, L._i, L._i, L._i, L._p])
 L.register("ib_selective_scan", [L._p, L._p, L._i, L._ll, L._p, L._i, L._ll, L._i, L._p, L._p, L._p, L._p, L._p, L._ll, L._p, L._ll, L._i, L._p, L._p, L._i, L._p, L._i,
-                                 L._i, L._i, L._i, L._p])
+                                 L._i, L._i, L._i, L._p, L._p, L._p, L._p, L._i, L._p])
+L.register("ib_scan_chunks_carry", [L._p, L._i, L._p, L._p, L._p, L._ll, L._p, L._p, L._p, L._p, L._i, L._ll, L._i, L._p, L._ll, L._i, L._i, L._i, L._p])
 
 
 def conv_silu(proj: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], conv_state: torch.Tensor, seg_of_token: torch.Tensor, seg_start: torch.Tensor,
@@ -827,8 +828,11 @@ def conv_silu(proj: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
 
 
 def selective_scan(xc: torch.Tensor, low: torch.Tensor, proj: torch.Tensor, wdt: torch.Tensor, dt_bias: torch.Tensor, A: torch.Tensor, D: torch.Tensor,
-                   state: torch.Tensor, conv_state: torch.Tensor, taps: int, seg_start: torch.Tensor, seg_slot: torch.Tensor, n_segments: int, out: torch.Tensor) -> None:
+                   state: torch.Tensor, conv_state: torch.Tensor, taps: int, seg_start: torch.Tensor, seg_slot: torch.Tensor, n_segments: int, out: torch.Tensor,
+                   seg_list: Optional[torch.Tensor] = None, long_segs: Optional[torch.Tensor] = None, chunks: Optional[torch.Tensor] = None) -> None:
     """The scan over every segment's tokens, from and into state (float32 [slots, inner, N]); also moves conv_state on to the segment's last taps - 1 inputs.
+    seg_list, long_segs, chunks: as for `gated_recurrence`: only the segments of seg_list are walked token by token, those of long_segs go chunk by
+    chunk (every chunk alone from a zero state, the states carried from chunk to chunk, every chunk again from its incoming state).
     xc float32 [T, inner]; low float32 partial sums [P, T, rank + 2 N] = [dt_low | B | C]; proj float32 partial sums [P, T, >= 2 inner] = [u | z];
     wdt float32 [inner, rank]; A float32 [inner, N] (negative rates); out [T, inner] = (y + D x) * silu(z)."""
     T, inner = xc.shape
@@ -845,6 +849,27 @@ def selective_scan(xc: torch.Tensor, low: torch.Tensor, proj: torch.Tensor, wdt:
     _check("state", state, torch.float32)
     _check("conv_state", conv_state, torch.float32)
     _check("out", out, None, (T, inner))
-    L.call("ib_selective_scan", xc.data_ptr(), low.data_ptr(), low.shape[0], T * low.shape[2], proj.data_ptr(), proj.shape[0], T * proj.shape[2], proj.shape[2],
-           wdt.data_ptr(), dt_bias.data_ptr(), A.data_ptr(), D.data_ptr(), state.data_ptr(), state.stride(0), conv_state.data_ptr(), conv_state.stride(0), int(taps),
-           seg_start.data_ptr(), seg_slot.data_ptr(), n_segments, out.data_ptr(), dtype_code(out.dtype), inner, N, rank, _stream())
+    def scan(n, segs, table, chunk_state, chunk_dt, which):
+        L.call("ib_selective_scan", xc.data_ptr(), low.data_ptr(), low.shape[0], T * low.shape[2], proj.data_ptr(), proj.shape[0], T * proj.shape[2], proj.shape[2],
+               wdt.data_ptr(), dt_bias.data_ptr(), A.data_ptr(), D.data_ptr(), state.data_ptr(), state.stride(0), conv_state.data_ptr(), conv_state.stride(0), int(taps),
+               seg_start.data_ptr(), seg_slot.data_ptr(), n, out.data_ptr(), dtype_code(out.dtype), inner, N, rank, _ptr(segs), _ptr(table), _ptr(chunk_state),
+               _ptr(chunk_dt), which, _stream())
+
+    if long_segs is None:
+        if seg_list is not None:
+            _check("seg_list", seg_list, torch.int32)
+            n_segments = seg_list.shape[0]
+        scan(n_segments, seg_list, None, None, None, 0)
+        return
+    _check("long_segs", long_segs, torch.int32)
+    _check("chunks", chunks, torch.int32)
+    if seg_list is not None and seg_list.shape[0]:
+        scan(seg_list.shape[0], seg_list, None, None, None, 0)
+    m = chunks.shape[0]
+    chunk_state = torch.empty((m, inner, N), dtype=torch.float32, device=xc.device)
+    chunk_dt = torch.empty((m, inner), dtype=torch.float32, device=xc.device)
+    scan(m, None, chunks, chunk_state, chunk_dt, 1)
+    L.call("ib_scan_chunks_carry", long_segs.data_ptr(), long_segs.shape[0], seg_start.data_ptr(), seg_slot.data_ptr(), state.data_ptr(), state.stride(0),
+           chunk_state.data_ptr(), chunk_dt.data_ptr(), A.data_ptr(), proj.data_ptr(), proj.shape[0], T * proj.shape[2], proj.shape[2], conv_state.data_ptr(),
+           conv_state.stride(0), int(taps), inner, N, _stream())
+    scan(m, None, chunks, chunk_state, chunk_dt, 2)

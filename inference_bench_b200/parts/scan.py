@@ -12,7 +12,9 @@ float32 sums of the product), the small product W_dt dt_low, softplus, the expon
 W_x and W_o read their inputs in the activation dtype.
 
 Kernels: csrc/selective_scan.cu (`conv_silu`, `selective_scan`; the scan also writes the new convolution state, after every reader of
-the old one).
+the old one). A segment of more than `ops.RECURRENCE_CHUNK` tokens is cut into chunks that are walked side by side: the decays of a
+chunk multiply to exp(A * sum of its step sizes), so each chunk is walked from a zero state, the states are carried from chunk to
+chunk, and each chunk is walked again from its incoming state for the outputs.
 """
 from __future__ import annotations
 
@@ -21,6 +23,7 @@ import torch
 from ..kernels import ops
 from . import base
 from .base import FixedState, Several, WeightSpec
+from .recurrent import GatedLinearRecurrence
 
 
 @base.register_mixer("mamba1")
@@ -62,5 +65,7 @@ class SelectiveScan(base.Mixer):
         ops.conv_silu(proj, self.conv_w, self.conv_b, conv_state, ctx.seg_of_token, ctx.seg_start, ctx.seg_slot, xc, None if xa is xc else xa)
         low = rt.linear(xa, self.w_x)                                           # [P, T, dt_rank + 2 state]
         y = rt.empty((T, self.inner))
-        ops.selective_scan(xc, low, proj, self.w_dt, self.dt_b, self.A, self.D, state, conv_state, self.taps, ctx.seg_start, ctx.seg_slot, ctx.n_segments, y)
+        short, long_segs, chunks = GatedLinearRecurrence._cut(ctx)            # one table of long segments and their chunks for all recurrences of a step
+        ops.selective_scan(xc, low, proj, self.w_dt, self.dt_b, self.A, self.D, state, conv_state, self.taps, ctx.seg_start, ctx.seg_slot, ctx.n_segments, y,
+                           seg_list=short, long_segs=long_segs, chunks=chunks)
         return rt.linear(y, self.w_o)

@@ -244,6 +244,49 @@ def test_selective_scan_over_portions_and_slots(dtype, inner, N, R, taps):
     rt.check_status()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("inner,N,R,taps", [(96, 5, 3, 4), (128, 40, 4, 3), (40, 150, 2, 1), (200, 16, 8, 5)])
+def test_selective_scan_long_portions_in_chunks(dtype, inner, N, R, taps):
+    """Portions longer than a chunk of the scan (walked chunk by chunk, side by side) beside short ones and single tokens, starting from a
+    zero state and from a state that earlier portions left, with lengths just below, at and above a multiple of the chunk; the slot of a
+    finished request is used again. Every row equals the plain scan of the whole sequence."""
+    from inference_bench_b200.cache.manager import StateView
+    from inference_bench_b200.engine.runtime import Runtime
+    from inference_bench_b200.kernels.ops import RECURRENCE_CHUNK as C
+    from inference_bench_b200.parts.scan import SelectiveScan
+    rt = Runtime(DEV, dtype=dtype)
+    W = 48
+    mixer = {"inner": inner, "state": N, "dt_rank": R, "conv": taps}
+    cfg = {"width": W, "vocab": 8, "layers": [{"type": "mamba1", "mixer": mixer, "mlp": None}]}
+    w = {n[len("l0."):]: t for n, t in tl.tensors(cfg, 3 * inner + N).items() if n.startswith("l0.mix")}
+    part = SelectiveScan("mix", W, inner, N, R, taps)
+    part.bind({n: t.to(DEV) for n, t in w.items()}, rt)
+    plan = [[("a", 2 * C + 2), ("b", 3)], [("a", 1), ("b", C + 1)], [("a", 3 * C), ("b", 1)], [("c", C), ("a", 1)], [("c", 4 * C - 1), ("a", C + 7)], [("c", 1)]]
+    lens = {}
+    for step in plan:
+        for r, n in step:
+            lens[r] = lens.get(r, 0) + n
+    g = torch.Generator().manual_seed(N + taps)
+    h = {r: torch.randn((n, W), generator=g).to(torch.bfloat16) for r, n in lens.items()}
+    want = {r: P.selective_scan_mixer(h[r].double(), w, "mix", mixer) for r in lens}
+    state, conv = torch.zeros((2, inner, N), device=DEV), torch.zeros((2, max(taps - 1, 1), inner), device=DEV)
+    slot, at = {"a": 0, "b": 1, "c": 1}, {r: 0 for r in lens}
+    tol = 3e-5 if dtype == "float32" else 4e-2
+    for step in plan:
+        if step[0][0] == "c" and at["c"] == 0:
+            state[1].zero_(), conv[1].zero_()
+        ctx = _ctx(rt, [(at[r], n) for r, n in step], [slot[r] for r, _ in step])
+        hs = torch.cat([h[r][at[r]:at[r] + n] for r, n in step]).to(DEV, rt.act_dtype).contiguous()
+        out = part.forward(ctx, hs, (StateView(state), StateView(conv))).sum(0).cpu().double()
+        o = 0
+        for r, n in step:
+            err = (out[o:o + n] - want[r][at[r]:at[r] + n]).abs().amax(dim=1) / want[r].abs().max().item()
+            assert err.max().item() < tol, f"request {r} rows {at[r]}..{at[r] + n}: row {at[r] + int(err.argmax())} differs by {err.max().item():.2e}"
+            o += n
+            at[r] += n
+    rt.check_status()
+
+
 # ------------------------------------------------------------------------------------------ whole models
 def _requests(name):
     vocab = tl.CONFIGS[name]["config"]["vocab"]
