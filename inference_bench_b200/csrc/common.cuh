@@ -84,6 +84,13 @@ __device__ __forceinline__ float tanh_fast(float x) {
   return 1.f - __fdividef(2.f, t + 1.f);
 }
 
+__device__ __forceinline__ float softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+// xIELU with its two coefficients ap = softplus(p) and an = 1/2 + softplus(q): ap z^2 + z / 2 for z > 0, an (exp(z) - 1 - z) + z / 2 otherwise.
+__device__ __forceinline__ float xielu(float z, float ap, float an) {
+  return z > 0.f ? __fmaf_rn(ap * z, z, 0.5f * z) : __fmaf_rn(an, expm1f(z) - z, 0.5f * z);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -28,6 +28,7 @@ constexpr int UMMA_K = 16;  // k per tcgen05.mma of kind::f16
 constexpr int kThreads = 192;
 constexpr int EPI_STORE = 0;   // float32 partial products
 constexpr int EPI_SWIGLU = 1;  // accumulator 0 = gate, accumulator 1 = up -> bfloat16 silu(gate) * up
+constexpr int EPI_XIELU = 3;   // one or two accumulators of plain rows -> bfloat16 xielu(product) with the two numbers of act_pq
 constexpr int EPI_SWIGLU_HALF = 2;  // one accumulator: rows 0-63 = 64 gate rows, rows 64-127 = the matching 64 up rows -> bfloat16 silu(gate) * up
 // (for a handful of tokens: as many CTAs as the plain product has, I / 64, so the weights stream as fast, and neither the
 // float32 [T, 2I] intermediate nor the SiLU-mul kernel exists)
@@ -48,7 +49,7 @@ template <int BN, int MT, int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
     gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x, void* __restrict__ out_, int T,
                         int N, int K, int ktiles_per_split, int second_off, unsigned long long wait_ns, int starve, unsigned* __restrict__ status,
-                        const int* __restrict__ grp_offsets, const int* __restrict__ grp_tiles, int n_groups, int grp_w_rows) {
+                        const int* __restrict__ grp_offsets, const int* __restrict__ grp_tiles, int n_groups, int grp_w_rows, const float* __restrict__ act_pq) {
   // grp_offsets != nullptr: the rows of x are regrouped (rows grp_offsets[e] .. grp_offsets[e + 1] belong to group e, whose matrix is rows
   // e * grp_w_rows .. of w) and blockIdx.x counts token tiles over all groups: grp_tiles[e] is the first tile of group e, grp_tiles[n_groups]
   // their number (the grid is an upper bound; the CTAs beyond it leave at once). A tile never crosses a group's end: rows past it are
@@ -184,8 +185,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     ok = __all_sync(0xffffffffu, ok);
     constexpr int CH = BN < 32 ? 16 : 32;
     const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
-    if (ok && EPI == EPI_STORE) {
+    if (ok && (EPI == EPI_STORE || EPI == EPI_XIELU)) {
       float* dst = (float*)out_ + (size_t)split * T * N;
+      __nv_bfloat16* dst_act = (__nv_bfloat16*)out_;   // EPI_XIELU: the whole k-range is this CTA's, the activation is applied here
+      float ap = 0.f, an = 0.f;
+      if constexpr (EPI == EPI_XIELU) ap = ib::softplus(act_pq[0]), an = 0.5f + ib::softplus(act_pq[1]);
 #pragma unroll 1
       for (int m = 0; m < MT; m++) {
         const int n = n0 + m * BM + q * 32 + lane;
@@ -206,7 +210,12 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
             for (int c = 0; c < CH; c++) {
               const int t = t0 + c0 + c;
-              if (t < t_end) dst[(size_t)t * N + n] = __uint_as_float(r[c]);
+              if (t < t_end) {
+                if constexpr (EPI == EPI_XIELU)
+                  dst_act[(size_t)t * N + n] = __float2bfloat16_rn(ib::xielu(__uint_as_float(r[c]), ap, an));
+                else
+                  dst[(size_t)t * N + n] = __uint_as_float(r[c]);
+              }
             }
           }
         }
@@ -305,7 +314,7 @@ struct Groups {   // regrouped rows (see the kernel): nullptr offsets = one matr
 
 template <int BN, int MT, int EPI>
 int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N, int K, int splits, int kt_per_split, int second_off,
-           unsigned* status, cudaStream_t stream, int starve = 0, Groups grp = Groups()) {
+           unsigned* status, cudaStream_t stream, int starve = 0, Groups grp = Groups(), const float* act_pq = nullptr) {
   using TL = Tile<BN, MT>;
   static bool configured = false;
   if (!configured) {
@@ -317,7 +326,7 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tx, void* out, int T, int N
   dim3 grid(grp.offsets ? T / BN + grp.n : (T + BN - 1) / BN, (N + cols_per_cta - 1) / cols_per_cta, splits);
   IB_CHECK_ARG(grid.y <= 65535, "gemm_tcgen05: N=%d gives more than 65535 row blocks", N);
   ib::launch(gemm_tcgen05_kernel<BN, MT, EPI>, grid, kThreads, TL::kSmemBytes, stream, tw, tx, out, T, N, K, kt_per_split, second_off, ib_wait_limit_ns(), starve, status,
-             grp.offsets, grp.tiles, grp.n, grp.w_rows);
+             grp.offsets, grp.tiles, grp.n, grp.w_rows, act_pq);
   IB_CHECK_LAUNCH("gemm_tcgen05");
   return 0;
 }
@@ -375,6 +384,34 @@ extern "C" int ib_test_gemm_tcgen05_starved(const void* x, const void* w, float*
   if (make_tmap(&tw, w, N, K, BM)) return 1;
   if (make_tmap(&tx, x, T, K, 16)) return 1;
   return launch<16, 1, EPI_STORE>(tw, tx, out, T, N, K, 1, total_kt, 0, status, stream, 1);
+}
+
+// x [T, K], w [N, K] bfloat16 -> act [T, N] bfloat16 = xielu(x w^T) with the two numbers pq (float32, on the device) of the activation: the
+// product with the activation in its epilogue. bn, wide: as for ib_gemm_tcgen05; the k-range is not split.
+extern "C" int ib_gemm_xielu_tcgen05(const void* x, const void* w, void* act, int T, int N, int K, int bn, int wide, const float* pq, unsigned* status,
+                                     cudaStream_t stream) {
+  if (T == 0 || N == 0) return 0;
+  if (check_common("gemm_xielu_tcgen05", x, w, T, N, K, bn)) return 1;
+  IB_CHECK_ARG(pq, "gemm_xielu_tcgen05: the activation's two numbers are missing");
+  const int total_kt = (K + BK - 1) / BK;
+  CUtensorMap tw, tx;
+  if (make_tmap(&tw, w, N, K, BM)) return 1;
+  if (make_tmap(&tx, x, T, K, bn)) return 1;
+  if (wide) {
+    switch (bn) {
+      case 128: return launch<128, 2, EPI_XIELU>(tw, tx, act, T, N, K, 1, total_kt, BM, status, stream, 0, Groups(), pq);
+      case 256: return launch<256, 2, EPI_XIELU>(tw, tx, act, T, N, K, 1, total_kt, BM, status, stream, 0, Groups(), pq);
+      default: return ib_set_error("gemm_xielu_tcgen05: 256 rows of w per CTA go with token tiles of 128 or 256, not %d", bn);
+    }
+  }
+  switch (bn) {
+    case 16: return launch<16, 1, EPI_XIELU>(tw, tx, act, T, N, K, 1, total_kt, 0, status, stream, 0, Groups(), pq);
+    case 32: return launch<32, 1, EPI_XIELU>(tw, tx, act, T, N, K, 1, total_kt, 0, status, stream, 0, Groups(), pq);
+    case 64: return launch<64, 1, EPI_XIELU>(tw, tx, act, T, N, K, 1, total_kt, 0, status, stream, 0, Groups(), pq);
+    case 128: return launch<128, 1, EPI_XIELU>(tw, tx, act, T, N, K, 1, total_kt, 0, status, stream, 0, Groups(), pq);
+    case 256: return launch<256, 1, EPI_XIELU>(tw, tx, act, T, N, K, 1, total_kt, 0, status, stream, 0, Groups(), pq);
+    default: return ib_set_error("gemm_xielu_tcgen05: token tile %d is not one of 16, 32, 64, 128, 256", bn);
+  }
 }
 
 // SwiGLU front half in one kernel: w [2*I, K] = gate rows then up rows; act [T, I] bfloat16 =

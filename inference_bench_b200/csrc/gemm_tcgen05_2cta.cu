@@ -28,6 +28,7 @@ constexpr int UMMA_K = 16;
 constexpr int kThreads = 192;
 constexpr int EPI_STORE = 0, EPI_SWIGLU = 1, EPI_ADD = 2;   // float32 out; bfloat16 silu(gate) * up; float32 out += product
 constexpr int EPI_QKV = 3;   // the q/k/v projection finished in the epilogue: per-head norm, rotation, queries out, keys and values into the cache
+constexpr int EPI_XIELU = 4;   // bfloat16 xielu(product) with the activation's two numbers (QkvEpi::act_pq)
 constexpr int kQkvHead = 128;   // head size of the EPI_QKV form: a head is 128 accumulator columns
 constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;   // clears the bit that tells the two CTAs of a pair apart in a shared::cluster address
 
@@ -108,6 +109,7 @@ struct QkvEpi {
   IbKvView kv;
   int write_kv;
   int heads;
+  const float* act_pq;   // EPI_XIELU only: the activation's two numbers (p, q), float32 on the device
 };
 
 // Persistent: each CTA pair walks tiles pair, pair + n_pairs, ... (token tiles vary fastest, so the
@@ -340,8 +342,11 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
           }
         }
-      } else if constexpr (EPI == EPI_STORE || EPI == EPI_ADD) {
+      } else if constexpr (EPI == EPI_STORE || EPI == EPI_ADD || EPI == EPI_XIELU) {
         float* dst = (float*)out_;
+        __nv_bfloat16* dst_act = (__nv_bfloat16*)out_;
+        float ap = 0.f, an = 0.f;
+        if constexpr (EPI == EPI_XIELU) ap = ib::softplus(qe.act_pq[0]), an = 0.5f + ib::softplus(qe.act_pq[1]);
 #pragma unroll 1
         for (int m = 0; m < MT; m++) {
           const int n = n_pair + m * 2 * BM + (int)rank * BM + q * 32 + lane;
@@ -361,7 +366,12 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
               for (int c = 0; c < 32; c++) {
                 const int t = t0 + c0 + c;
-                if (t < T) dst[(size_t)t * N + n] = __uint_as_float(r[c]);
+                if (t < T) {
+                  if constexpr (EPI == EPI_XIELU)
+                    dst_act[(size_t)t * N + n] = __float2bfloat16_rn(ib::xielu(__uint_as_float(r[c]), ap, an));
+                  else
+                    dst[(size_t)t * N + n] = __uint_as_float(r[c]);
+                }
               }
             }
           }
@@ -469,6 +479,16 @@ extern "C" int ib_gemm_tcgen05_2cta(const void* x, const void* w, float* out, in
 extern "C" int ib_gemm_tcgen05_2cta_add(const void* x, const void* w, float* out, int T, int N, int K, unsigned* status, cudaStream_t stream) {
   if (T == 0 || N == 0) return 0;
   return launch<1, EPI_ADD, 256>(x, w, out, T, N, K, N, 0, status, stream);
+}
+
+// x [T, K], w [N, K] bfloat16 -> act [T, N] bfloat16 = xielu(x w^T) with the two numbers pq (float32, on the device): the product of
+// ib_gemm_tcgen05_2cta with the activation in its epilogue.
+extern "C" int ib_gemm_xielu_tcgen05_2cta(const void* x, const void* w, void* act, int T, int N, int K, const float* pq, unsigned* status, cudaStream_t stream) {
+  if (T == 0 || N == 0) return 0;
+  IB_CHECK_ARG(pq, "gemm_xielu_tcgen05_2cta: the activation's two numbers are missing");
+  QkvEpi qe{};
+  qe.act_pq = pq;
+  return launch<1, EPI_XIELU, 256>(x, w, act, T, N, K, N, 0, status, stream, qe);
 }
 
 // w [2*I, K] = gate rows then up rows -> act [T, I] bfloat16 = silu(x gate^T) * (x up^T), on CTA pairs.

@@ -15,7 +15,6 @@
 
 namespace {
 
-__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.f / (1.f + expf(-z)); }
 
 template <typename O>
@@ -109,13 +108,12 @@ __global__ void xielu_rows_kernel(const float* __restrict__ z, int P, size_t str
   ib::pdl_launch_dependents();
   ib::pdl_wait();
   const int t = blockIdx.y;
-  const float ap = softplus_f(pq[0]), an = 0.5f + softplus_f(pq[1]);
+  const float ap = ib::softplus(pq[0]), an = 0.5f + ib::softplus(pq[1]);
   const float* row = z + (size_t)t * I;
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < I; i += gridDim.x * blockDim.x) {
     float v = row[i];
     for (int p = 1; p < P; p++) v += row[p * stride + i];
-    const float y = v > 0.f ? __fmaf_rn(ap * v, v, 0.5f * v) : __fmaf_rn(an, expm1f(v) - v, 0.5f * v);
-    act[(size_t)t * I + i] = ib::from_f32<O>(y);
+    act[(size_t)t * I + i] = ib::from_f32<O>(ib::xielu(v, ap, an));
   }
 }
 

@@ -119,6 +119,22 @@ class Runtime:
         ops.silu_mul(gu, act)
         return act
 
+    def up_xielu(self, x: torch.Tensor, lw: LinearWeights, pq: torch.Tensor) -> torch.Tensor:
+        """x [T, K] -> xielu(x W^T) in the activation dtype, [T, N], with the activation's two numbers pq (float32 [2]). bfloat16 products
+        that need not cut their k-range apply the activation in the tensor-core kernel's epilogue, on the float32 accumulators;
+        otherwise the product and the row-wise kernel that adds the partial sums."""
+        T = x.shape[0]
+        if self.mode == "bfloat16" and self.gemm != "simt" and self.options.swiglu_epilogue:
+            from ..kernels import gemm_tcgen05
+            if gemm_tcgen05.xielu_in_epilogue(T, lw.n, lw.k, self.sm_count):
+                act = self.empty((T, lw.n))
+                gemm_tcgen05.gemm_xielu(self, x, lw, pq, act)
+                return act
+        z = self.linear(x, lw)
+        act = self.empty((T, lw.n))
+        ops.xielu_rows(z, pq, act)
+        return act
+
     # ---------------------------------------------------------------- status word
     def check_status(self) -> None:
         """Read the status word (synchronises) and raise if a kernel reported a fault."""

@@ -23,6 +23,8 @@ L.register("ib_gemm_tcgen05", [L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L
 L.register("ib_gemm_swiglu_tcgen05", [L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._p, L._p])
 L.register("ib_gemm_tcgen05_2cta", [L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
 L.register("ib_gemm_swiglu_tcgen05_2cta", [L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
+L.register("ib_gemm_xielu_tcgen05", [L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._p, L._p, L._p])
+L.register("ib_gemm_xielu_tcgen05_2cta", [L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p, L._p])
 L.register("ib_gemm_tcgen05_2cta_add", [L._p, L._p, L._p, L._i, L._i, L._i, L._p, L._p])
 L.register("ib_gemm_qkv_tcgen05_2cta", [L._p, L._p, L._i, L._i, L._p, L._p, L._f, L._p, L._p, L._p, L._p, L._p, C.POINTER(L.KvView), L._i, L._i, L._p, L._p])
 
@@ -248,6 +250,34 @@ def gemm_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, act: torch.Tensor, sta
     if bn is None:
         bn = 64 if T <= 64 else (128 if T <= 128 else 256)
     L.call("ib_gemm_swiglu_tcgen05", x.data_ptr(), w_gate_up.data_ptr(), act.data_ptr(), T, I, K, bn, 1 if half else 0, status.data_ptr(), ops._stream())
+
+
+XIELU_MIN_ROW_BLOCKS = 32   # 128-row blocks of the matrix from which up to 128 tokens keep the whole k-range in one CTA (that many CTAs fill the memory system)
+
+
+def xielu_in_epilogue(T: int, N: int, K: int, sm_count: int = FITTED_SM_COUNT) -> bool:
+    """Whether the product of T tokens with an [N, K] matrix applies the xIELU activation in its epilogue: above 128 tokens always; up to
+    128 when the matrix has enough row blocks to fill the GPU without cutting the k-range (otherwise the k-range is split over CTAs and
+    `ops.xielu_rows` adds the partial sums). A function of the sizes only."""
+    if not supports(K):
+        return False
+    return T > 128 or -(-N // 128) >= XIELU_MIN_ROW_BLOCKS or choose(T, N, K, True, sm_count)[1] == 1
+
+
+def gemm_xielu(rt, x: torch.Tensor, lw, pq: torch.Tensor, act: torch.Tensor) -> None:
+    """act [T, N] bfloat16 = xielu(x w^T) with pq = (p, q) float32 on the device; the kernel's form is chosen like `linear`'s, without
+    cutting the k-range."""
+    T, K = x.shape
+    ops._check("x", x, torch.bfloat16)
+    ops._check("w", lw.weight, torch.bfloat16, (lw.n, K))
+    ops._check("act", act, torch.bfloat16, (T, lw.n))
+    ops._check("pq", pq, torch.float32, (2,))
+    how = ("pair",) if T >= rt.options.pair_always_tokens else (plan(T, lw.n, K, rt.sm_count, False) if T > 128 else None)
+    if how is not None and how[0] == "pair":
+        L.call("ib_gemm_xielu_tcgen05_2cta", x.data_ptr(), lw.weight.data_ptr(), act.data_ptr(), T, lw.n, K, pq.data_ptr(), rt.status.data_ptr(), ops._stream())
+        return
+    bn, _, wide = how[1:] if how is not None else choose(T, lw.n, K, False, rt.sm_count)
+    L.call("ib_gemm_xielu_tcgen05", x.data_ptr(), lw.weight.data_ptr(), act.data_ptr(), T, lw.n, K, bn, 1 if wide else 0, pq.data_ptr(), rt.status.data_ptr(), ops._stream())
 
 
 # ---------------------------------------------------------------- products on regrouped rows (routed experts)

@@ -289,7 +289,7 @@ class SwiGLU(base.FeedForward):
 class DenseXielu(base.FeedForward):
     """down(act(up h)) with the activation xIELU, whose two numbers (p, q) are a tensor of the layer:
     act(z) = softplus(p) z^2 + z / 2 for z > 0, (1/2 + softplus(q)) (exp(z) - 1 - z) + z / 2 otherwise, in float32 on the product's
-    float32 sums."""
+    float32 sums (`Runtime.up_xielu`: in the tensor-core product's epilogue where its k-range is whole)."""
 
     def __init__(self, prefix: str, hidden: int, intermediate: int, names: tuple = ("up", "down", "act")):
         self.prefix, self.hidden, self.intermediate, self.names = prefix, hidden, intermediate, tuple(names)
@@ -308,10 +308,7 @@ class DenseXielu(base.FeedForward):
 
     def forward(self, ctx, h, residual=None):
         rt = ctx.rt
-        z = rt.linear(h, self.wu)
-        act = rt.empty((h.shape[0], self.intermediate))
-        ops.xielu_rows(z, self.pq, act)
-        return rt.linear(act, self.wd, add_to=residual)
+        return rt.linear(rt.up_xielu(h, self.wu, self.pq), self.wd, add_to=residual)
 
 
 # ------------------------------------------------------------------------------------------ embedding and head

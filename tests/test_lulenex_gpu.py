@@ -208,6 +208,41 @@ def test_norm_with_a_bias_xielu_gated_norm_and_loop_entry(rt32):
 
 
 # ------------------------------------------------------------------------------------------ the selective scan with its convolution
+@pytest.mark.parametrize("T,N,K", [(1, 4096, 64), (8, 4224, 1024), (5, 200, 72), (17, 136, 264), (64, 5000, 520), (100, 4096, 136), (128, 130, 64),
+                                   (8, 256, 2048), (129, 520, 264), (300, 1000, 1024), (700, 8192, 256), (2048, 384, 512), (2300, 1100, 72)])
+def test_product_with_xielu_in_its_epilogue(rt16, T, N, K):
+    """The up projection with the activation applied to the float32 accumulators in the tensor-core kernels (one CTA a tile for few
+    tokens, CTA pairs for many; sizes that end inside a tile), against float64, and against the product followed by the row-wise
+    kernel; both signs of the activation's two numbers."""
+    from inference_bench_b200.kernels import gemm_tcgen05 as G
+    from inference_bench_b200.kernels import lib as L
+    from inference_bench_b200.kernels import ops
+    g = torch.Generator().manual_seed(T + N + K)
+    x = (torch.randn(T, K, generator=g) * 0.7).to(torch.bfloat16).to(DEV)
+    lw = rt16.matrix((torch.randn(N, K, generator=g) * (2.0 / math.sqrt(K))).to(torch.bfloat16))
+    for pq in ((0.8, -0.4), (-1.5, 2.0)):
+        pq_dev = _f32(torch.tensor(pq))
+        called = []
+        real = L.call
+        L.call = lambda name, *a: (called.append(name), real(name, *a))[1]
+        try:
+            act = rt16.up_xielu(x, lw, pq_dev)
+        finally:
+            L.call = real
+        if G.xielu_in_epilogue(T, N, K, rt16.sm_count):
+            assert called in (["ib_gemm_xielu_tcgen05"], ["ib_gemm_xielu_tcgen05_2cta"])
+            assert called == ["ib_gemm_xielu_tcgen05"] if T <= 128 else T < 2048 or called == ["ib_gemm_xielu_tcgen05_2cta"]
+        else:
+            assert (T, N, K) == (8, 256, 2048) and called[-1] == "ib_xielu_rows"
+        want = P.xielu(x.cpu().double() @ lw.weight.cpu().double().T, torch.tensor(pq, dtype=torch.float64))
+        assert ((act.cpu().double() - want).abs() <= 2.0 ** -8 * want.abs() + 2e-5 * want.abs().max()).all()
+        z = rt16.linear(x, lw)
+        rows = torch.empty((T, N), dtype=torch.bfloat16, device=DEV)
+        ops.xielu_rows(z, pq_dev, rows)
+        assert ((act.float() - rows.float()).abs() <= 2.0 ** -7 * rows.float().abs() + 1e-6).all()
+    rt16.check_status()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("inner,N,R,taps", [(96, 5, 3, 4), (60, 17, 1, 1), (128, 40, 4, 3), (72, 16, 8, 2), (40, 150, 2, 5), (36, 1, 2, 2)])
 def test_selective_scan_over_portions_and_slots(dtype, inner, N, R, taps):
