@@ -492,6 +492,8 @@ LULENEX_SIZES = {
                   experts=8, top=2, expert_ff=1408),
     "mid": dict(width=2048, heads=16, kv_heads=4, dim=128, chunk=1536, rec_heads=16, rec_dim=128, rec_vdim=128, inner=4096, state=16, dt_rank=128, conv=4, ff=8192, vocab=32768,
                 experts=8, top=2, expert_ff=2688),
+    "large": dict(width=4096, heads=32, kv_heads=8, dim=128, chunk=1536, rec_heads=32, rec_dim=128, rec_vdim=128, inner=8192, state=16, dt_rank=256, conv=4, ff=16384, vocab=32768,
+                  experts=8, top=2, expert_ff=5504),
 }
 
 
