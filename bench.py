@@ -492,6 +492,9 @@ LULENEX_SIZES = {
                   experts=8, top=2, expert_ff=1408),
     "mid": dict(width=2048, heads=16, kv_heads=4, dim=128, chunk=1536, rec_heads=16, rec_dim=128, rec_vdim=128, inner=4096, state=16, dt_rank=128, conv=4, ff=8192, vocab=32768,
                 experts=8, top=2, expert_ff=2688),
+}
+# A third size, run on its own (`--size large`): it is not among the default sizes.
+LULENEX_EXTRA_SIZES = {
     "large": dict(width=4096, heads=32, kv_heads=8, dim=128, chunk=1536, rec_heads=32, rec_dim=128, rec_vdim=128, inner=8192, state=16, dt_rank=256, conv=4, ff=16384, vocab=32768,
                   experts=8, top=2, expert_ff=5504),
 }
@@ -645,7 +648,7 @@ def run_design(args) -> dict:
     out = {"design": args.design, "layers": layers, "peaks": pk_src, "sizes": {}}
     sizes = {"busadra": BUSADRA_SIZES, "lulenex": LULENEX_SIZES}.get(args.design, DESIGN_SIZES)
     for name in (args.size.split(",") if args.size else list(sizes)):
-        z = sizes[name]
+        z = sizes[name] if name in sizes or args.design != "lulenex" else LULENEX_EXTRA_SIZES[name]
         report = {}
         if args.design == "lulenex":
             zb = dict(z, window=z["chunk"])
