@@ -20,6 +20,7 @@ _CHOICES = {
     "prefill_attention": ("auto", "ws", "tcgen05"),
     "decode_attention": ("auto", "stream", "split"),
     "latent_attention": ("auto", "generic", "mma"),
+    "sigmoid_attention": ("auto", "generic", "mma"),
     "expert_gemm": ("auto", "simt", "mma", "tcgen05"),
 }
 _ALIASES = {"dtype": {"bf16": "bfloat16", "fp32": "float32"}}
@@ -48,6 +49,7 @@ class RuntimeOptions:
     stream_tiles_per_slice: int = 0    # 0: each token's keys in equal slices; n > 0: slices of n tiles at fixed positions
     split_tiles_per_slice: int = 0     # 0: chosen from the step's sizes; n > 0: fixed
     latent_attention: str = "auto"     # latent attention: "mma": the tensor-core kernel (bfloat16, row sizes that are multiples of 16); "generic": the FMA kernel; "auto": mma where it fits
+    sigmoid_attention: str = "auto"    # attention with sigmoid weights: "mma": the tensor-core kernel (bfloat16, head sizes that are multiples of 16, up to 16 heads a kv head); "generic": the FMA kernel; "auto": mma where it fits
     expert_gemm: str = "auto"          # routed experts' products: "tcgen05" (bfloat16, inner sizes that are multiples of 8), "mma" (m16n8k16, the same sizes; also the per-head maps of latent attention), "simt": FMA chains; "auto": the first that fits
     # ---- cache and scheduler
     page_size: int = 64

@@ -47,6 +47,27 @@ __global__ void embed_kernel(const W* __restrict__ table, const int* __restrict_
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < H; i += gridDim.x * blockDim.x) dst[i] = ib::to_f32<W>(src[i]);
 }
 
+// x[t] = table[token] * scale + pos_table[position]: an embedding with a constant on the token's vector and a learned vector per position
+// (not scaled). A position outside the table counts as a bad token (its vector is left out).
+template <typename W>
+__global__ void embed_pos_kernel(const W* __restrict__ table, const int* __restrict__ tokens, const W* __restrict__ pos_table, const int* __restrict__ positions,
+                                 float scale, float* __restrict__ x, int H, int V, int max_pos, unsigned* __restrict__ status) {
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
+  int t = blockIdx.y;
+  int tok = tokens[t], pos = positions[t];
+  if (tok < 0 || tok >= V || pos < 0 || pos >= max_pos) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) atomicOr(status, IB_ERR_BAD_TOKEN);
+    if (tok < 0 || tok >= V) tok = 0;
+    if (pos < 0 || pos >= max_pos) pos = -1;
+  }
+  const W* src = table + (size_t)tok * H;
+  const W* ps = pos_table + (size_t)(pos < 0 ? 0 : pos) * H;
+  float* dst = x + (size_t)t * H;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < H; i += gridDim.x * blockDim.x)
+    dst[i] = __fmaf_rn(ib::to_f32<W>(src[i]), scale, pos < 0 ? 0.f : ib::to_f32<W>(ps[i]));
+}
+
 // ---------------------------------------------------------------- residual add + RMSNorm
 // One block per output row r. Source row t = rows ? rows[r] : r.
 //   v = x[t] + sum_p delta[p][t]   (partials summed in order p = 0..P-1, then added to x)
@@ -287,6 +308,49 @@ __global__ void norm_residual_kernel(float* __restrict__ x, const float* __restr
   }
 }
 
+// A sublayer's output through a norm of its own, added to the stream, and the next sublayer's input norm, in one pass over the row.
+// One block per output row r; source row t = rows ? rows[r] : r.
+//   y = sum_p delta[p][t] + bias;   v = x[t] + w_post * (y * rsqrt(mean(y^2) + eps))        (without delta: v = x[t])
+//   x[t] = v  (unless rows gathers);   out[r] = w_next * (v * rsqrt(mean(v^2) + eps))       (without out: the add alone)
+// The row lives in shared memory between the passes; all arithmetic float32, sums in an order that depends on H alone.
+template <typename O>
+__global__ void post_norm_kernel(float* __restrict__ x, const float* __restrict__ delta, int P, size_t delta_stride, const float* __restrict__ bias,
+                                 const float* __restrict__ w_post, const float* __restrict__ w_next, float eps, O* __restrict__ out,
+                                 const int* __restrict__ rows, int H) {
+  extern __shared__ __align__(16) float row[];
+  __shared__ float scratch[32];
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
+  const int r = blockIdx.x, t = rows ? rows[r] : r;
+  float* xr = x + (size_t)t * H;
+  float inv = 0.f;
+  if (delta) {
+    const float* dr = delta + (size_t)t * H;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      float d = dr[i];
+      for (int p = 1; p < P; p++) d += dr[p * delta_stride + i];
+      if (bias) d += bias[i];
+      row[i] = d;
+      ss = __fmaf_rn(d, d, ss);
+    }
+    ss = ib::block_sum(ss, scratch);
+    inv = 1.f / sqrtf(ss / (float)H + eps);
+  }
+  float s2 = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = xr[i];
+    if (delta) v += w_post[i] * (row[i] * inv);
+    if (!rows) xr[i] = v;
+    row[i] = v;
+    s2 = __fmaf_rn(v, v, s2);
+  }
+  if (!out) return;
+  s2 = ib::block_sum(s2, scratch);
+  const float inv2 = 1.f / sqrtf(s2 / (float)H + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) out[(size_t)r * H + i] = ib::from_f32<O>(w_next[i] * (row[i] * inv2));
+}
+
 // act[t] = x[t] in another dtype.
 template <typename O>
 __global__ void cast_rows_kernel(const float* __restrict__ x, O* __restrict__ act, size_t n) {
@@ -399,6 +463,42 @@ extern "C" int ib_norm_residual(float* x, const float* delta, int P, long long d
   else if (act_dtype == IB_BF16) go(norm_residual_kernel<__nv_bfloat16>, (__nv_bfloat16*)act);
   else return ib_set_error("norm_residual: unknown activation dtype %d", act_dtype);
   IB_CHECK_LAUNCH("norm_residual");
+  return 0;
+}
+
+extern "C" int ib_post_norm(float* x, const float* delta, int P, long long delta_stride, const float* bias, const float* w_post, const float* w_next, float eps,
+                            void* out, int out_dtype, const int* rows, int n_rows, int H, cudaStream_t stream) {
+  // delta null: no contribution (w_post and bias are then not read); out null: the add alone; rows: gather (x is left as it is).
+  if (n_rows == 0) return 0;
+  IB_CHECK_ARG(n_rows > 0 && H > 0 && (!delta || (P >= 1 && w_post)) && (!out || w_next) && (delta || out), "post_norm: bad arguments rows=%d H=%d P=%d", n_rows, H, P);
+  const size_t smem = (size_t)H * sizeof(float);
+  IB_CHECK_ARG(smem <= 200 * 1024, "post_norm: hidden size %d needs %zu bytes of shared memory, more than 200 KiB", H, smem);
+  const int threads = H >= 2048 ? 1024 : (H >= 1024 ? 512 : 256);
+  auto go = [&](auto kernel, auto* o) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ib::launch(kernel, n_rows, threads, smem, stream, x, delta, P, (size_t)delta_stride, bias, w_post, w_next, eps, o, rows, H);
+  };
+  if (!out || out_dtype == IB_F32) go(post_norm_kernel<float>, (float*)out);
+  else if (out_dtype == IB_BF16) go(post_norm_kernel<__nv_bfloat16>, (__nv_bfloat16*)out);
+  else return ib_set_error("post_norm: unknown output dtype %d", out_dtype);
+  IB_CHECK_LAUNCH("post_norm");
+  return 0;
+}
+
+extern "C" int ib_embed_pos(const void* table, int table_dtype, const int* tokens, const void* pos_table, const int* positions, float scale, float* x, int T, int H,
+                            int V, int max_pos, unsigned* status, cudaStream_t stream) {
+  if (T == 0) return 0;
+  IB_CHECK_ARG(T > 0 && H > 0 && V > 0 && max_pos > 0 && pos_table && positions, "embed_pos: bad sizes T=%d H=%d V=%d positions=%d", T, H, V, max_pos);
+  IB_CHECK_ARG(T <= 65535, "embed_pos: T=%d rows exceed the grid limit 65535", T);
+  dim3 grid((H + 1023) / 1024 > 0 ? (H + 1023) / 1024 : 1, T);
+  if (table_dtype == IB_F32)
+    ib::launch(embed_pos_kernel<float>, grid, 256, 0, stream, (const float*)table, tokens, (const float*)pos_table, positions, scale, x, H, V, max_pos, status);
+  else if (table_dtype == IB_BF16)
+    ib::launch(embed_pos_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)table, tokens, (const __nv_bfloat16*)pos_table, positions, scale, x, H, V,
+               max_pos, status);
+  else
+    return ib_set_error("embed_pos: unknown table dtype %d", table_dtype);
+  IB_CHECK_LAUNCH("embed_pos");
   return 0;
 }
 

@@ -31,6 +31,11 @@ struct RowsArgs {
   int rows;      // heads mode: T
   int N, K;
   int grouped;
+  // heads mode: float32 partial sums [gate_P][T][gate_row], offset to the first head's column, or null: head b's output of row t is multiplied
+  // by the sigmoid of its column
+  const float* gate;
+  int gate_P, gate_row;
+  long long gate_stride;
 };
 
 template <bool GATED, typename O>
@@ -157,6 +162,13 @@ __global__ void __launch_bounds__(128) gemm_rows_mma_kernel(RowsArgs p) {
       const int row = r0 + wm * 32 + m * 16 + g + 8 * h;
       if (row >= r1) continue;
       O* dst = p.grouped ? out + (size_t)row * N : out + (size_t)row * p.o_row + (size_t)group * p.o_head;
+      float f = 1.f;
+      if (!p.grouped && p.gate) {
+        const float* gr = p.gate + (size_t)row * p.gate_row + group;
+        float z = gr[0];
+        for (int q = 1; q < p.gate_P; q++) z += gr[q * p.gate_stride];
+        f = 1.f / (1.f + expf(-z));
+      }
 #pragma unroll
       for (int nt = 0; nt < 4; nt++)
 #pragma unroll
@@ -165,7 +177,7 @@ __global__ void __launch_bounds__(128) gemm_rows_mma_kernel(RowsArgs p) {
           if (n >= N) continue;
           float v = acc[m][nt][2 * h + c];
           if constexpr (GATED) v = (v / (1.f + expf(-v))) * acu[m][nt][2 * h + c];
-          dst[n] = ib::from_f32<O>(v);
+          dst[n] = ib::from_f32<O>(v * f);
         }
     }
 }
@@ -201,12 +213,13 @@ extern "C" int ib_gemm_grouped_mma(const void* x, const int* src_row, const void
 }
 
 extern "C" int ib_gemm_heads_mma(const void* x, long long x_row, long long x_head, const void* w, void* out, int out_dtype, long long o_row, long long o_head, int T,
-                                 int heads, int N, int K, cudaStream_t stream) {
+                                 int heads, int N, int K, const float* gate, int gate_P, long long gate_stride, int gate_row, cudaStream_t stream) {
   if (T == 0 || N == 0 || heads == 0) return 0;
   IB_CHECK_ARG(T > 0 && N > 0 && K > 0 && heads > 0, "gemm_heads_mma: bad sizes T=%d heads=%d N=%d K=%d", T, heads, N, K);
   IB_CHECK_ARG(x_row % 8 == 0 && x_head % 8 == 0, "gemm_heads_mma: row stride %lld and head stride %lld must be multiples of 8", x_row, x_head);
   RowsArgs a = {};
   a.x = (const __nv_bfloat16*)x, a.w = (const __nv_bfloat16*)w, a.out = out, a.x_row = x_row, a.x_head = x_head, a.o_row = o_row, a.o_head = o_head;
   a.rows = T, a.N = N, a.K = K, a.grouped = 0;
+  a.gate = gate, a.gate_P = gate_P, a.gate_stride = gate_stride, a.gate_row = gate_row;
   return launch_rows(a, dim3((N + TN - 1) / TN, (T + TM - 1) / TM, heads), 0, out_dtype, stream, "gemm_heads_mma");
 }

@@ -93,12 +93,74 @@ __global__ void latent_prepare_kernel(const float* __restrict__ qd, int P, size_
   }
 }
 
+// The first product of a layer whose queries go through a latent of their own: [c_q raw (q_rank) | c raw (rank) | key part (rot) | ...].
+// Warp 0 of a token norms c_q (weight w_q) into the activation dtype, the operand of the product that makes the heads' queries; warp 1
+// norms the latent, rotates the shared key part and writes the token's cache row. Further columns (gates) are left to their readers.
+template <typename A, typename C>
+__global__ void latent_down_kernel(const float* __restrict__ qd, int P, size_t stride_p, int row_len, int q_rank, const float* __restrict__ q_norm_w,
+                                   A* __restrict__ cq, const float* __restrict__ c_norm_w, float eps, const float* __restrict__ cos_t,
+                                   const float* __restrict__ sin_t, int rot_half, const int* __restrict__ positions, const int* __restrict__ seg_of_token,
+                                   IbKvView kv, int rank, int rot, unsigned* __restrict__ status) {
+  ib::pdl_launch_dependents();
+  ib::pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const float* row = qd + (size_t)t * row_len;
+  auto summed = [&](int col) {
+    float a = row[col];
+    for (int p = 1; p < P; p++) a += row[p * stride_p + col];
+    return a;
+  };
+  if (warp == 0) {
+    float ss = 0.f;
+    for (int d = lane; d < q_rank; d += 32) {
+      const float a = summed(d);
+      ss = __fmaf_rn(a, a, ss);
+    }
+    ss = ib::warp_sum(ss);
+    const float inv = 1.f / sqrtf(ss / (float)q_rank + eps);
+    for (int d = lane; d < q_rank; d += 32) cq[(size_t)t * q_rank + d] = ib::from_f32<A>(summed(d) * inv * q_norm_w[d]);
+    return;
+  }
+  const long long off = ib::kv_offset(kv, seg_of_token[t], positions[t], 0);
+  if (off < 0) {
+    if (lane == 0) atomicOr(status, IB_ERR_BAD_PAGE);
+    return;
+  }
+  C* dst = (C*)kv.base + off;
+  const int col0 = q_rank;
+  float ss = 0.f;
+  for (int d = lane; d < rank; d += 32) {
+    const float a = summed(col0 + d);
+    ss = __fmaf_rn(a, a, ss);
+  }
+  ss = ib::warp_sum(ss);
+  const float inv = 1.f / sqrtf(ss / (float)rank + eps);
+  for (int d = lane; d < rank; d += 32) dst[d] = ib::from_f32<C>(summed(col0 + d) * inv * c_norm_w[d]);
+  const float* cs = cos_t + (size_t)t * rot_half;
+  const float* sn = sin_t + (size_t)t * rot_half;
+  for (int i = lane; 2 * i < rot; i += 32) {
+    const float a = summed(col0 + rank + 2 * i), b = 2 * i + 1 < rot ? summed(col0 + rank + 2 * i + 1) : 0.f;
+    float x = a, y = b;
+    if (i < rot_half) {
+      const float c = cs[i], s = sn[i];
+      x = a * c - b * s;
+      y = b * c + a * s;
+    }
+    dst[rank + 2 * i] = ib::from_f32<C>(x);
+    if (2 * i + 1 < rot) dst[rank + 2 * i + 1] = ib::from_f32<C>(y);
+  }
+}
+
 // ---------------------------------------------------------------- per-head products
 constexpr int GM = 64, GN = 64, GK = 16;
 
 template <typename X, typename W, typename O>
 __global__ void __launch_bounds__(256) gemm_heads_kernel(const X* __restrict__ x, long long x_row, long long x_head, const W* __restrict__ w,
-                                                         O* __restrict__ out, long long o_row, long long o_head, int T, int N, int K) {
+                                                         O* __restrict__ out, long long o_row, long long o_head, int T, int N, int K,
+                                                         const float* __restrict__ gate, int gate_P, size_t gate_stride, int gate_row) {
+  // gate: float32 partial sums [gate_P][T][gate_row], offset to the first head's column, or null: head b's output of token t is multiplied by
+  // the sigmoid of its column.
   __shared__ float xs[GK][GM + 1];
   __shared__ float ws[GK][GN + 1];
   ib::pdl_launch_dependents();
@@ -140,10 +202,17 @@ __global__ void __launch_bounds__(256) gemm_heads_kernel(const X* __restrict__ x
   for (int i = 0; i < 4; i++) {
     const int t = t0 + ty * 4 + i;
     if (t >= T) continue;
+    float f = 1.f;
+    if (gate) {
+      const float* gr = gate + (size_t)t * gate_row + b;
+      float z = gr[0];
+      for (int p = 1; p < gate_P; p++) z += gr[p * gate_stride];
+      f = 1.f / (1.f + expf(-z));
+    }
 #pragma unroll
     for (int j = 0; j < 4; j++) {
       const int n = n0 + tx * 4 + j;
-      if (n < N) out[(size_t)t * o_row + (size_t)b * o_head + n] = ib::from_f32<O>(acc[i][j]);
+      if (n < N) out[(size_t)t * o_row + (size_t)b * o_head + n] = ib::from_f32<O>(acc[i][j] * f);
     }
   }
 }
@@ -154,7 +223,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) latent_attention_kernel(const
                                                                            const int* __restrict__ seg_of_token, float scale, O* __restrict__ out,
                                                                            float* __restrict__ part_o, float* __restrict__ part_ml, int T, int H,
                                                                            int rank, int D, int n_slices, int slice_keys,
-                                                                           unsigned* __restrict__ status) {
+                                                                           unsigned* __restrict__ status, int window) {
+  // window > 0: a token sees itself and the window - 1 positions before it; the slices then cut that range.
   extern __shared__ __align__(16) float smem[];
   __shared__ long long koff[kKeyTile];
   float* qs = smem;                          // [kAttnWarps][D]
@@ -165,7 +235,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) latent_attention_kernel(const
   const int t = blockIdx.y, h = blockIdx.x * kAttnWarps + warp, slice = blockIdx.z;
   const bool live = h < H;
   const int pos = positions[t], seg = seg_of_token[t];
-  const int lo = slice * slice_keys;
+  const int lo = (window > 0 ? max(0, pos - window + 1) : 0) + slice * slice_keys;
   const int hi = min(pos, lo + slice_keys - 1);   // last key of this slice (inclusive); lo > hi: nothing to see
   const int KS = D + 1;
   if (live) {
@@ -307,13 +377,35 @@ extern "C" int ib_latent_prepare(const float* qd, int P, long long stride_p, int
   return 0;
 }
 
+extern "C" int ib_latent_down(const float* qd, int P, long long stride_p, int row_len, int q_rank, const float* q_norm_w, void* cq, int act_dtype,
+                              const float* c_norm_w, float eps, const float* cos_t, const float* sin_t, int rot_half, const int* positions,
+                              const int* seg_of_token, const IbKvView* kv, int rank, int rot, int T, unsigned* status, cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (check_rows_view("latent_down", kv)) return 1;
+  IB_CHECK_ARG(P >= 1 && q_rank > 0 && rank > 0 && rot >= 0 && q_norm_w && c_norm_w && cq, "latent_down: bad sizes P=%d q_rank=%d rank=%d rot=%d", P, q_rank, rank, rot);
+  IB_CHECK_ARG(kv->head_dim == rank + rot, "latent_down: the cache row has %d values, expected rank + rot = %d", kv->head_dim, rank + rot);
+  IB_CHECK_ARG(2 * rot_half <= rot && row_len >= q_rank + rank + rot, "latent_down: a row of %d columns does not hold %d + %d + %d (turned: %d)", row_len, q_rank, rank,
+               rot, 2 * rot_half);
+  auto go = [&](auto kernel, auto* out) {
+    ib::launch(kernel, (unsigned)T, 64, 0, stream, qd, P, (size_t)stride_p, row_len, q_rank, q_norm_w, out, c_norm_w, eps, cos_t, sin_t, rot_half, positions, seg_of_token,
+               *kv, rank, rot, status);
+  };
+  if (act_dtype == IB_F32 && kv->dtype == IB_F32) go(latent_down_kernel<float, float>, (float*)cq);
+  else if (act_dtype == IB_BF16 && kv->dtype == IB_BF16) go(latent_down_kernel<__nv_bfloat16, __nv_bfloat16>, (__nv_bfloat16*)cq);
+  else return ib_set_error("latent_down: activation dtype %d and cache dtype %d must match", act_dtype, kv->dtype);
+  IB_CHECK_LAUNCH("latent_down");
+  return 0;
+}
+
 extern "C" int ib_gemm_heads(const void* x, int x_dtype, long long x_row, long long x_head, const void* w, int w_dtype, void* out, int out_dtype,
-                             long long o_row, long long o_head, int T, int heads, int N, int K, cudaStream_t stream) {
+                             long long o_row, long long o_head, int T, int heads, int N, int K, const float* gate, int gate_P, long long gate_stride,
+                             int gate_row, cudaStream_t stream) {
+  // gate: float32 partial sums [gate_P][T][gate_row] offset to the first head's column (head b of token t is multiplied by the sigmoid of its column), or null.
   if (T == 0 || N == 0 || heads == 0) return 0;
   IB_CHECK_ARG(T > 0 && N > 0 && K > 0 && heads > 0, "gemm_heads: bad sizes T=%d heads=%d N=%d K=%d", T, heads, N, K);
   dim3 grid((N + GN - 1) / GN, (T + GM - 1) / GM, heads);
   IB_CHECK_ARG(grid.y <= 65535 && grid.z <= 65535, "gemm_heads: T=%d or heads=%d exceed the grid limit", T, heads);
-  auto go = [&](auto kernel, auto* xp, auto* wp, auto* op) { ib::launch(kernel, grid, 256, 0, stream, xp, x_row, x_head, wp, op, o_row, o_head, T, N, K); };
+  auto go = [&](auto kernel, auto* xp, auto* wp, auto* op) { ib::launch(kernel, grid, 256, 0, stream, xp, x_row, x_head, wp, op, o_row, o_head, T, N, K, gate, gate_P, (size_t)gate_stride, gate_row); };
   using bf = __nv_bfloat16;
   if (x_dtype == IB_F32 && w_dtype == IB_F32 && out_dtype == IB_F32) go(gemm_heads_kernel<float, float, float>, (const float*)x, (const float*)w, (float*)out);
   else if (x_dtype == IB_BF16 && w_dtype == IB_BF16 && out_dtype == IB_F32) go(gemm_heads_kernel<bf, bf, float>, (const bf*)x, (const bf*)w, (float*)out);
@@ -337,7 +429,7 @@ extern "C" int ib_latent_combine(const float* part_o, const float* part_ml, void
 
 extern "C" int ib_latent_attention(const float* q, const IbKvView* kv, const int* positions, const int* seg_of_token, float scale, void* out,
                                    int out_dtype, float* part_o, float* part_ml, int T, int heads, int rank, int n_slices, int slice_keys,
-                                   unsigned* status, cudaStream_t stream) {
+                                   unsigned* status, int window, cudaStream_t stream) {
   if (T == 0) return 0;
   if (check_rows_view("latent_attention", kv)) return 1;
   const int D = kv->head_dim;
@@ -351,7 +443,7 @@ extern "C" int ib_latent_attention(const float* q, const IbKvView* kv, const int
   auto go = [&](auto kernel, auto* o) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ib::launch(kernel, grid, kAttnWarps * 32, smem, stream, q, *kv, positions, seg_of_token, scale, o, part_o, part_ml, T, heads, rank, D, n_slices, slice_keys,
-               status);
+               status, window);
   };
   auto pick = [&](auto c_tag, auto* o) {
     using C = decltype(c_tag);

@@ -29,7 +29,9 @@ template <int NCH, int MT>
 __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(const float* __restrict__ q, IbKvView kv, const int* __restrict__ positions,
                                                                            const int* __restrict__ seg_of_token, const int2* __restrict__ units, float scale,
                                                                            __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
-                                                                           int H, int rank, int D, int n_slices, int slice_keys, unsigned* __restrict__ status) {
+                                                                           int H, int rank, int D, int n_slices, int slice_keys, unsigned* __restrict__ status,
+                                                                           int window) {
+  // window > 0: a token sees itself and the window - 1 positions before it; the CTA's keys start where its first token's window does.
   constexpr int R = 16 * MT;                                 // query rows of the CTA
   extern __shared__ __align__(128) unsigned char smem[];
   const int blocks = (D + 63) / 64;                          // 64-value blocks of a row
@@ -54,8 +56,9 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(const
   const int slice = blockIdx.z;
   const int seg = seg_of_token[tok0];
   const int last_pos = positions[tok0 + ntok - 1];
-  const int lo = slice * slice_keys;
+  const int lo = (window > 0 ? max(0, positions[tok0] - window + 1) : 0) + slice * slice_keys;
   const int hi = min(last_pos, lo + slice_keys - 1);
+  const int reach = window > 0 ? window : 0x7fffffff;   // a row at position p sees keys above p - reach
   // the rows this thread sees in its accumulators: g + 8 e of every 16-row tile
   int row_pos[MT][2], row_tok[MT][2], row_head[MT][2];
 #pragma unroll
@@ -185,7 +188,7 @@ __global__ void __launch_bounds__(kWarps * 32) latent_attention_mma_kernel(const
 #pragma unroll
       for (int e = 0; e < 4; e++) {
         const int key = k0 + kKeysPerWarp * warp + 2 * t4 + (e & 1), rr = e >> 1;
-        const float v = (key <= hi && key <= row_pos[a][rr]) ? s[a][e] * scale : -INFINITY;
+        const float v = (key <= hi && key <= row_pos[a][rr] && row_pos[a][rr] - key < reach) ? s[a][e] * scale : -INFINITY;
         s[a][e] = v;
         mx[rr] = fmaxf(mx[rr], v);
       }
@@ -333,7 +336,7 @@ extern "C" int ib_latent_attention_mma_rows(int rank, int D, int rows_wanted) {
 
 extern "C" int ib_latent_attention_mma(const float* q, const IbKvView* kv, const int* positions, const int* seg_of_token, const int* units, int n_units, int rows,
                                        float scale, void* out, float* part_o, float* part_ml, int T, int heads, int rank, int n_slices, int slice_keys,
-                                       unsigned* status, cudaStream_t stream) {
+                                       unsigned* status, int window, cudaStream_t stream) {
   if (T == 0 || n_units == 0) return 0;
   IB_CHECK_ARG(kv && kv->base && kv->block_table && kv->kv_heads == 1 && kv->dtype == IB_BF16, "latent_attention_mma: a bfloat16 cache of one row per token is needed");
   const int D = kv->head_dim;
@@ -352,7 +355,7 @@ extern "C" int ib_latent_attention_mma(const float* q, const IbKvView* kv, const
   auto go = [&](auto kernel) {
     if (smem > 40 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ib::launch(kernel, grid, kWarps * 32, smem, stream, q, *kv, positions, seg_of_token, (const int2*)units, scale, (__nv_bfloat16*)out, part_o, part_ml, heads, rank, D,
-               n_slices, slice_keys, status);
+               n_slices, slice_keys, status, window);
   };
   auto pick = [&](auto nch) {
     constexpr int NCH = decltype(nch)::value;

@@ -3,9 +3,10 @@
 //
 //  * moe_route: per token, s = softmax(router logits) over all experts in float32 (or, with `score` = 1, s = sigmoid of each logit
 //    on its own); experts lie in `n_groups` equal
-//    groups of neighbours, a group's score is its largest s, only the `keep` best groups stay eligible; the `top`
+//    groups of neighbours, a group's score is its largest s (or the sum of its few largest), only the `keep` best groups stay eligible; the `top`
 //    eligible experts with the largest s are chosen (ties: the lower index), each weighted s * route_scale, or
-//    s / (sum of the chosen s) * route_scale with `renorm`.
+//    s / (sum of the chosen s) * route_scale with `renorm`. With a correction, groups and experts are chosen by s + correction[e]
+//    and weighted by s alone.
 //  * moe_sort: counts the (token, choice) pairs of every expert, lays the experts' rows out one after the other
 //    (offsets[e] .. offsets[e + 1]) and gives every pair a row of its expert's range; tile_start[e] is the first tile of expert e.
 //  * gemm_grouped: out[r] = W[e(r)] x[src(r)] for every regrouped row r: a 64 x 64 tile belongs to one expert; float32
@@ -33,15 +34,20 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
 }
 
 __global__ void moe_route_kernel(const float* __restrict__ logits, int P, size_t stride_p, int T, int E, int n_groups, int keep, int top, float route_scale,
-                                 int renorm, int* __restrict__ idx_out, float* __restrict__ wt_out, int score) {
-  extern __shared__ float sm[];   // per warp: E scores, then n_groups group scores
+                                 int renorm, int* __restrict__ idx_out, float* __restrict__ wt_out, int score, const float* __restrict__ correction,
+                                 int group_top) {
+  // correction: a number per expert added to its score for the choice (of groups and of experts) and left out of the weights, or null.
+  // group_top: a group's score is the sum of its `group_top` largest choice scores (1: its largest).
+  // Choice scores may be negative: what cannot be chosen counts as minus infinity.
+  extern __shared__ float sm[];   // per warp: E scores, E choice scores, then n_groups group scores
   ib::pdl_launch_dependents();
   ib::pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * kRouteWarps + warp;
   if (t >= T) return;
-  float* s = sm + (size_t)warp * (E + n_groups);
-  float* g = s + E;
+  float* s = sm + (size_t)warp * (2 * E + n_groups);
+  float* c = s + E;
+  float* g = c + E;
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) {
     float z = logits[(size_t)t * E + e];
@@ -63,42 +69,56 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int P, size_t
     const float inv = 1.f / sum;
     for (int e = lane; e < E; e += 32) s[e] *= inv;
   }
+  for (int e = lane; e < E; e += 32) c[e] = correction ? s[e] + correction[e] : s[e];
   __syncwarp();
   if (n_groups > 1 && keep < n_groups) {
     const int per = E / n_groups;
     for (int k = lane; k < n_groups; k += 32) {
-      float b = -1.f;
-      for (int e = k * per; e < (k + 1) * per; e++) b = fmaxf(b, s[e]);
-      g[k] = b;
+      // the group's `group_top` largest choice scores, found one after the other (ties: the lower index first, which changes no sum)
+      float total = 0.f;
+      int taken[4] = {-1, -1, -1, -1};
+      for (int r = 0; r < group_top && r < per; r++) {
+        float b = -INFINITY;
+        int bi = -1;
+        for (int e = k * per; e < (k + 1) * per; e++) {
+          if (e == taken[0] || e == taken[1] || e == taken[2] || e == taken[3]) continue;
+          if (bi < 0 || c[e] > b) b = c[e], bi = e;
+        }
+        taken[r] = bi;
+        total += b;
+      }
+      g[k] = total;
     }
     __syncwarp();
-    for (int r = 0; r < keep; r++) {   // the best groups, one after the other; a kept group's score becomes -2
-      float bv = -1.5f;
+    for (int r = 0; r < keep; r++) {   // the best groups, one after the other; a kept group is marked in `g` by NaN
+      float bv = -INFINITY;
       int bi = 0x7fffffff;
       for (int k = lane; k < n_groups; k += 32)
-        if (g[k] > bv) bv = g[k], bi = k;
+        if (g[k] == g[k] && (bi == 0x7fffffff || g[k] > bv)) bv = g[k], bi = k;
       warp_argmax(bv, bi);
-      if (lane == 0 && bi < n_groups) g[bi] = -2.f;
+      if (lane == 0 && bi < n_groups) g[bi] = __int_as_float(0x7fc00000);
       __syncwarp();
     }
     for (int e = lane; e < E; e += 32)
-      if (g[e / per] != -2.f) s[e] = -1.f;   // not eligible
+      if (g[e / per] == g[e / per]) c[e] = -INFINITY;   // its group was not kept
     __syncwarp();
   }
   float chosen_sum = 0.f;
   for (int r = 0; r < top; r++) {
-    float bv = -0.5f;
+    float bv = -INFINITY;
     int bi = 0x7fffffff;
     for (int e = lane; e < E; e += 32)
-      if (s[e] > bv) bv = s[e], bi = e;
+      if (c[e] > bv) bv = c[e], bi = e;
     warp_argmax(bv, bi);
-    if (bi >= E) bi = 0, bv = 0.f;   // fewer eligible experts than choices: weight zero
+    float w = 0.f;
+    if (bi >= E) bi = 0;   // fewer experts that can be chosen than choices: weight zero
+    else w = s[bi];
     if (lane == 0) {
       idx_out[(size_t)t * top + r] = bi;
-      wt_out[(size_t)t * top + r] = bv;
-      s[bi] = -1.f;
+      wt_out[(size_t)t * top + r] = w;
+      c[bi] = -INFINITY;
     }
-    chosen_sum += bv;
+    chosen_sum += w;
     __syncwarp();
   }
   if (lane == 0) {
@@ -286,15 +306,17 @@ __global__ void scatter_scaled_rows_kernel(const X* __restrict__ x, const int* _
 }  // namespace
 
 extern "C" int ib_moe_route(const float* logits, int P, long long stride_p, int T, int E, int n_groups, int keep, int top, float route_scale, int renorm,
-                            int* idx_out, float* wt_out, int score, cudaStream_t stream) {
+                            int* idx_out, float* wt_out, int score, const float* correction, int group_top, cudaStream_t stream) {
+  // correction: float32 [E] added to the scores for the choice only, or null; group_top: how many of a group's largest choice scores make its score (1 to 4).
   if (T == 0) return 0;
+  IB_CHECK_ARG(group_top >= 1 && group_top <= 4, "moe_route: a group's score is the sum of its %d largest scores (1 to 4)", group_top);
   IB_CHECK_ARG(P >= 1 && E > 0 && top > 0 && top <= E, "moe_route: bad sizes P=%d experts=%d top=%d", P, E, top);
   IB_CHECK_ARG(score == 0 || score == 1, "moe_route: score %d is neither 0 (softmax) nor 1 (sigmoid)", score);
   IB_CHECK_ARG(n_groups >= 1 && E % n_groups == 0 && keep >= 1 && keep <= n_groups, "moe_route: %d experts in %d groups of which %d stay", E, n_groups, keep);
-  const size_t smem = (size_t)kRouteWarps * (E + n_groups) * sizeof(float);
+  const size_t smem = (size_t)kRouteWarps * (2 * E + n_groups) * sizeof(float);
   IB_CHECK_ARG(smem <= 48 * 1024, "moe_route: %d experts need %zu bytes of shared memory, more than 48 KiB", E, smem);
   ib::launch(moe_route_kernel, (unsigned)((T + kRouteWarps - 1) / kRouteWarps), kRouteWarps * 32, smem, stream, logits, P, (size_t)stride_p, T, E, n_groups, keep,
-             top, route_scale, renorm, idx_out, wt_out, score);
+             top, route_scale, renorm, idx_out, wt_out, score, correction, group_top);
   IB_CHECK_LAUNCH("moe_route");
   return 0;
 }

@@ -124,6 +124,51 @@ def embed(table: torch.Tensor, tokens: torch.Tensor, x: torch.Tensor, status: to
     L.call("ib_embed", table.data_ptr(), dtype_code(table.dtype), tokens.data_ptr(), x.data_ptr(), T, H, V, status.data_ptr(), _stream())
 
 
+L.register("ib_embed_pos", [L._p, L._i, L._p, L._p, L._p, L._f, L._p, L._i, L._i, L._i, L._i, L._p, L._p])
+L.register("ib_post_norm", [L._p, L._p, L._i, L._ll, L._p, L._p, L._p, L._f, L._p, L._i, L._p, L._i, L._i, L._p])
+
+
+def embed_pos(table: torch.Tensor, tokens: torch.Tensor, pos_table: torch.Tensor, positions: torch.Tensor, scale: float, x: torch.Tensor, status: torch.Tensor) -> None:
+    """x[t] = float32(table[tokens[t]]) * scale + float32(pos_table[positions[t]]): a learned vector per position beside the token's."""
+    V, H = table.shape
+    T = tokens.shape[0]
+    _check("table", table)
+    _check("pos_table", pos_table, table.dtype)
+    if pos_table.shape[1] != H:
+        raise L.KernelError(f"embed_pos: the position table has {pos_table.shape[1]} columns, the token table {H}")
+    _check("tokens", tokens, torch.int32)
+    _check("positions", positions, torch.int32, (T,))
+    _check("x", x, torch.float32, (T, H))
+    L.call("ib_embed_pos", table.data_ptr(), dtype_code(table.dtype), tokens.data_ptr(), pos_table.data_ptr(), positions.data_ptr(), float(scale), x.data_ptr(), T, H, V,
+           pos_table.shape[0], status.data_ptr(), _stream())
+
+
+def post_norm(x: torch.Tensor, delta: Optional[torch.Tensor], bias: Optional[torch.Tensor], w_post: Optional[torch.Tensor], w_next: Optional[torch.Tensor],
+              out: Optional[torch.Tensor], eps: float, rows: Optional[torch.Tensor] = None) -> None:
+    """x += w_post * rms_unit(sum_p delta[p] + bias) (in place, unless `rows` gathers), then out = w_next * rms_unit(x): a sublayer's
+    output through its own norm into the stream, and the next sublayer's input norm, in one kernel. delta None: no contribution;
+    out None: the add alone. With `rows` (int32 [n]) output row r comes from source row rows[r] and x is left as it is."""
+    T, H = x.shape
+    _check("x", x, torch.float32)
+    n_rows = T if rows is None else rows.shape[0]
+    P, stride = 0, 0
+    if delta is not None:
+        _check("delta", delta, torch.float32)
+        if delta.dim() != 3 or tuple(delta.shape[1:]) != (T, H):
+            raise L.KernelError(f"post_norm: delta must be [P, {T}, {H}], got {tuple(delta.shape)}")
+        P, stride = delta.shape[0], T * H
+        _check("w_post", w_post, torch.float32, (H,))
+        if bias is not None:
+            _check("bias", bias, torch.float32, (H,))
+    if out is not None:
+        _check("out", out, None, (n_rows, H))
+        _check("w_next", w_next, torch.float32, (H,))
+    if rows is not None:
+        _check("rows", rows, torch.int32)
+    L.call("ib_post_norm", x.data_ptr(), _ptr(delta), P, stride, _ptr(bias) if delta is not None else None, _ptr(w_post), _ptr(w_next), float(eps), _ptr(out),
+           dtype_code(out.dtype) if out is not None else 0, _ptr(rows), n_rows, H, _stream())
+
+
 def add_rmsnorm(x: torch.Tensor, delta: Optional[torch.Tensor], w: torch.Tensor, out: torch.Tensor, eps: float,
                 rows: Optional[torch.Tensor] = None) -> None:
     """x += sum_p delta[p] (in place, unless `rows` gathers); out = w * (x * rsqrt(mean(x^2) + eps)).
@@ -302,8 +347,9 @@ def cast_rows(x: torch.Tensor, act: torch.Tensor) -> None:
 # ---------------------------------------------------------------- latent attention (csrc/latent_attention.cu)
 L.register("ib_latent_prepare", [L._p, L._i, L._ll, L._i, L._p, L._f, L._p, L._p, L._i, L._p, L._p, L._p, L._i, L._p, C.POINTER(L.KvView), L._i, L._i, L._i, L._i,
                                  L._i, L._i, L._p, L._p])
-L.register("ib_gemm_heads", [L._p, L._i, L._ll, L._ll, L._p, L._i, L._p, L._i, L._ll, L._ll, L._i, L._i, L._i, L._i, L._p])
-L.register("ib_latent_attention", [L._p, C.POINTER(L.KvView), L._p, L._p, L._f, L._p, L._i, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._p, L._p])
+L.register("ib_gemm_heads", [L._p, L._i, L._ll, L._ll, L._p, L._i, L._p, L._i, L._ll, L._ll, L._i, L._i, L._i, L._i, L._p, L._i, L._ll, L._i, L._p])
+L.register("ib_latent_attention", [L._p, C.POINTER(L.KvView), L._p, L._p, L._f, L._p, L._i, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._p, L._i, L._p])
+L.register("ib_latent_down", [L._p, L._i, L._ll, L._i, L._i, L._p, L._p, L._i, L._p, L._f, L._p, L._p, L._i, L._p, L._p, C.POINTER(L.KvView), L._i, L._i, L._i, L._p, L._p])
 L.KERNELS_PER_CALL["ib_latent_attention"] = 1   # two with slices; counted by the caller
 
 
@@ -333,7 +379,28 @@ def latent_prepare(qd: torch.Tensor, c_norm_w: Optional[torch.Tensor], eps: floa
 
 
 L.register("ib_gemm_grouped_mma", [L._p, L._p, L._p, L._p, L._i, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._p])
-L.register("ib_gemm_heads_mma", [L._p, L._ll, L._ll, L._p, L._p, L._i, L._ll, L._ll, L._i, L._i, L._i, L._i, L._p])
+L.register("ib_gemm_heads_mma", [L._p, L._ll, L._ll, L._p, L._p, L._i, L._ll, L._ll, L._i, L._i, L._i, L._i, L._p, L._i, L._ll, L._i, L._p])
+
+
+def latent_down(qd: torch.Tensor, q_rank: int, q_norm_w: torch.Tensor, cq: torch.Tensor, c_norm_w: torch.Tensor, eps: float, cos: Optional[torch.Tensor],
+                sin: Optional[torch.Tensor], positions: torch.Tensor, seg_of_token: torch.Tensor, kv: KvLayerView, rank: int, rot: int, status: torch.Tensor) -> None:
+    """qd float32 [P, T, >= q_rank + rank + rot]: partial sums of a layer's first product [query latent | latent | key part | ...].
+    -> cq [T, q_rank] (activation dtype): the normed query latent, and the token's cache row [normed latent | rotated key part]."""
+    _check("qd", qd, torch.float32)
+    P, T, R = qd.shape
+    _check("cq", cq, None, (T, q_rank))
+    _check("q_norm_w", q_norm_w, torch.float32, (q_rank,))
+    _check("c_norm_w", c_norm_w, torch.float32, (rank,))
+    _check("positions", positions, torch.int32, (T,))
+    _check("seg_of_token", seg_of_token, torch.int32, (T,))
+    rot_half = 0
+    if cos is not None:
+        rot_half = cos.shape[1]
+        _check("cos", cos, torch.float32, (T, rot_half))
+        _check("sin", sin, torch.float32, (T, rot_half))
+    view = kv.c_view()
+    L.call("ib_latent_down", qd.data_ptr(), P, T * R, R, int(q_rank), q_norm_w.data_ptr(), cq.data_ptr(), dtype_code(cq.dtype), c_norm_w.data_ptr(), float(eps),
+           _ptr(cos), _ptr(sin), rot_half, positions.data_ptr(), seg_of_token.data_ptr(), C.byref(view), int(rank), int(rot), T, status.data_ptr(), _stream())
 
 
 def rows_mma_fits(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -341,10 +408,19 @@ def rows_mma_fits(x: torch.Tensor, w: torch.Tensor) -> bool:
     return x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
 
 
-def gemm_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n: int, tensor_cores: bool = False) -> None:
+def gemm_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n: int, tensor_cores: bool = False, gate: Optional[tuple] = None) -> None:
     """out[t, b, :n] = w[b] x[t, b] for every head b: x [T, heads, K] (contiguous), w [heads, N, K], out [T, heads, >= n] whose
-    first n columns of every head are written (the rest stay). tensor_cores: the m16n8k16 kernel (see `rows_mma_fits`)."""
+    first n columns of every head are written (the rest stay). tensor_cores: the m16n8k16 kernel (see `rows_mma_fits`).
+    gate = (float32 partial sums [P, T, row], column of the first head): head b's output is multiplied by the sigmoid of its column."""
     T, heads, K = x.shape
+    g_ptr, g_P, g_stride, g_row = None, 0, 0, 0
+    if gate is not None:
+        g, col = gate
+        _check("gate", g, torch.float32)
+        g_P, g_row = g.shape[0], g.shape[2]
+        if g.dim() != 3 or g.shape[1] != T or col + heads > g_row:
+            raise L.KernelError(f"gemm_heads: the gate's partial sums {tuple(g.shape)} do not hold {heads} columns from {col} for {T} tokens")
+        g_ptr, g_stride = g.data_ptr() + 4 * col, T * g_row
     _check("x", x)
     _check("w", w, None, (heads, n, K))
     _check("out", out)
@@ -354,16 +430,17 @@ def gemm_heads(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, n: int, tens
         if not rows_mma_fits(x, w):
             raise L.KernelError("gemm_heads: the tensor-core kernel needs bfloat16 operands with an inner size that is a multiple of 8")
         L.call("ib_gemm_heads_mma", x.data_ptr(), heads * K, K, w.data_ptr(), out.data_ptr(), dtype_code(out.dtype), heads * out.shape[2], out.shape[2], T, heads, n, K,
-               _stream())
+               g_ptr, g_P, g_stride, g_row, _stream())
         return
     L.call("ib_gemm_heads", x.data_ptr(), dtype_code(x.dtype), heads * K, K, w.data_ptr(), dtype_code(w.dtype), out.data_ptr(), dtype_code(out.dtype),
-           heads * out.shape[2], out.shape[2], T, heads, n, K, _stream())
+           heads * out.shape[2], out.shape[2], T, heads, n, K, g_ptr, g_P, g_stride, g_row, _stream())
 
 
 def latent_attention(q_full: torch.Tensor, kv: KvLayerView, positions: torch.Tensor, seg_of_token: torch.Tensor, scale: float, out: torch.Tensor, rank: int,
-                     n_slices: int, slice_keys: int, scratch, status: torch.Tensor) -> None:
+                     n_slices: int, slice_keys: int, scratch, status: torch.Tensor, window: Optional[int] = None) -> None:
     """q_full float32 [T, heads, row] against the cached rows [latent (rank) | key part]: out [T, heads, rank] = softmax-weighted sum of
-    the latents of the keys a token sees (all up to its own position). scratch: (part_o, part_ml) float32 when n_slices > 1."""
+    the latents of the keys a token sees (all up to its own position, or with `window` itself and the window - 1 before it; the slices
+    then cut that range). scratch: (part_o, part_ml) float32 when n_slices > 1."""
     T, heads, D = q_full.shape
     _check("q_full", q_full, torch.float32)
     _check("out", out, None, (T, heads, rank))
@@ -380,10 +457,10 @@ def latent_attention(q_full: torch.Tensor, kv: KvLayerView, positions: torch.Ten
             raise L.KernelError("latent_attention: the scratch for the slices is too small")
         L.launches += 1
     L.call("ib_latent_attention", q_full.data_ptr(), C.byref(view), positions.data_ptr(), seg_of_token.data_ptr(), float(scale), out.data_ptr(),
-           dtype_code(out.dtype), _ptr(part_o), _ptr(part_ml), T, heads, rank, n_slices, slice_keys, status.data_ptr(), _stream())
+           dtype_code(out.dtype), _ptr(part_o), _ptr(part_ml), T, heads, rank, n_slices, slice_keys, status.data_ptr(), int(window or 0), _stream())
 
 
-L.register("ib_latent_attention_mma", [L._p, C.POINTER(L.KvView), L._p, L._p, L._p, L._i, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._p, L._p])
+L.register("ib_latent_attention_mma", [L._p, C.POINTER(L.KvView), L._p, L._p, L._p, L._i, L._i, L._f, L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._p, L._i, L._p])
 
 
 def latent_attention_mma_rows(rank: int, row: int, rows_wanted: int) -> int:
@@ -396,7 +473,8 @@ def latent_attention_mma_supports(rank: int, row: int) -> bool:
 
 
 def latent_attention_mma(q_full: torch.Tensor, kv: KvLayerView, positions: torch.Tensor, seg_of_token: torch.Tensor, units: Optional[torch.Tensor], scale: float,
-                         out: torch.Tensor, rank: int, n_slices: int, slice_keys: int, scratch, status: torch.Tensor, rows: int = 16) -> None:
+                         out: torch.Tensor, rank: int, n_slices: int, slice_keys: int, scratch, status: torch.Tensor, rows: int = 16,
+                         window: Optional[int] = None) -> None:
     """The same as `latent_attention` on the tensor cores (bfloat16 cache and output). rows: query rows a CTA holds (16, 32 or 64).
     units: None (a CTA per token) or int32 [n, 2] of (first token, tokens): runs of consecutive tokens of one request that share a
     CTA's rows (at most rows // heads tokens each)."""
@@ -418,11 +496,11 @@ def latent_attention_mma(q_full: torch.Tensor, kv: KvLayerView, positions: torch
             raise L.KernelError("latent_attention_mma: the scratch for the slices is too small")
         L.launches += 1
     L.call("ib_latent_attention_mma", q_full.data_ptr(), C.byref(view), positions.data_ptr(), seg_of_token.data_ptr(), _ptr(units), n_units, int(rows), float(scale),
-           out.data_ptr(), _ptr(part_o), _ptr(part_ml), T, heads, rank, n_slices, slice_keys, status.data_ptr(), _stream())
+           out.data_ptr(), _ptr(part_o), _ptr(part_ml), T, heads, rank, n_slices, slice_keys, status.data_ptr(), int(window or 0), _stream())
 
 
 # ---------------------------------------------------------------- routed experts (csrc/moe.cu)
-L.register("ib_moe_route", [L._p, L._i, L._ll, L._i, L._i, L._i, L._i, L._i, L._f, L._i, L._p, L._p, L._i, L._p])
+L.register("ib_moe_route", [L._p, L._i, L._ll, L._i, L._i, L._i, L._i, L._i, L._f, L._i, L._p, L._p, L._i, L._p, L._i, L._p])
 L.register("ib_scatter_scaled_rows", [L._p, L._i, L._p, L._p, L._i, L._p, L._i, L._i, L._p])
 L.register("ib_moe_sort", [L._p, L._i, L._i, L._i, L._i, L._p, L._p, L._p, L._p, L._p])
 L.register("ib_gather_rows", [L._p, L._p, L._p, L._i, L._i, L._i, L._p])
@@ -447,16 +525,20 @@ L.register("ib_moe_combine", [L._p, L._p, L._p, L._i, L._p, L._i, L._ll, L._p, L
 
 
 def moe_route(logits: torch.Tensor, n_groups: int, keep: int, top: int, route_scale: float, renorm: bool, idx: torch.Tensor, wt: torch.Tensor,
-              score: str = "softmax") -> None:
+              score: str = "softmax", correction: Optional[torch.Tensor] = None, group_top: int = 1) -> None:
     """logits float32 [P, T, E] (partial sums) -> idx int32 [T, top], wt float32 [T, top]. score: "softmax" over all experts, or
-    "sigmoid" of every expert's logit on its own."""
+    "sigmoid" of every expert's logit on its own. correction: float32 [E] added to the scores where groups and experts are chosen (the
+    weights are the scores without it). group_top: a group's score is the sum of its `group_top` largest choice scores (1: the largest)."""
     if score not in ("softmax", "sigmoid"):
         raise L.KernelError(f"moe_route: score {score!r} is not known (softmax, sigmoid)")
     _check("logits", logits, torch.float32)
     P, T, E = logits.shape
     _check("idx", idx, torch.int32, (T, top))
     _check("wt", wt, torch.float32, (T, top))
-    L.call("ib_moe_route", logits.data_ptr(), P, T * E, T, E, n_groups, keep, top, float(route_scale), 1 if renorm else 0, idx.data_ptr(), wt.data_ptr(), 1 if score == "sigmoid" else 0, _stream())
+    if correction is not None:
+        _check("correction", correction, torch.float32, (E,))
+    L.call("ib_moe_route", logits.data_ptr(), P, T * E, T, E, n_groups, keep, top, float(route_scale), 1 if renorm else 0, idx.data_ptr(), wt.data_ptr(),
+           1 if score == "sigmoid" else 0, _ptr(correction), int(group_top), _stream())
 
 
 def moe_sort(idx: torch.Tensor, n_experts: int, offsets: torch.Tensor, tile_start: torch.Tensor, row_of_pair: torch.Tensor, token_of_row: torch.Tensor,
@@ -873,3 +955,88 @@ def selective_scan(xc: torch.Tensor, low: torch.Tensor, proj: torch.Tensor, wdt:
            chunk_state.data_ptr(), chunk_dt.data_ptr(), A.data_ptr(), proj.data_ptr(), proj.shape[0], T * proj.shape[2], proj.shape[2], conv_state.data_ptr(),
            conv_state.stride(0), int(taps), inner, N, _stream())
     scan(m, None, chunks, chunk_state, chunk_dt, 2)
+
+
+# ---------------------------------------------------------------- attention with sigmoid weights behind a convolution of its projections (csrc/sigmoid_attention.cu)
+L.register("ib_qkv_conv", [L._p, L._i, L._ll, L._p, L._p, L._i, L._p, L._ll, L._p, L._p, L._p, L._i, L._p, L._i, L._i, L._i, L._i, L._f, L._i, L._i, L._f, L._p, L._i,
+                           C.POINTER(L.KvView), L._p, L._p])
+L.register("ib_sigmoid_attention", [L._p, L._i, C.POINTER(L.KvView), L._p, L._p, L._f, L._p, L._p, L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._i, L._p, L._p])
+L.register("ib_sigmoid_attention_mma", [L._p, C.POINTER(L.KvView), L._p, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._i, L._p, L._p])
+L.KERNELS_PER_CALL["ib_qkv_conv"] = 1   # two with a convolution state; counted by the caller
+
+
+def qkv_conv(proj: torch.Tensor, bias: Optional[torch.Tensor], conv_w: Optional[torch.Tensor], conv_state: Optional[torch.Tensor], seg_of_token: torch.Tensor,
+             seg_start: torch.Tensor, seg_slot: torch.Tensor, n_segments: int, positions: torch.Tensor, q_out: torch.Tensor, kv: KvLayerView, heads: int, qk_dim: int,
+             v_dim: int, status: torch.Tensor, q_temp: Optional[tuple] = None, v_norm: bool = False, eps: float = 0.0) -> None:
+    """proj float32 [P, T, R] with R = [heads x qk_dim | kv_heads x qk_dim | kv_heads x v_dim], bias float32 [R] or None.
+    conv_w float32 [taps, R] (a tap's weights for all channels together; the last row is the current token's) or None for no convolution;
+    conv_state float32 [slots, taps - 1, R]: the last rows of the biased projection of every request, read for the rows before a segment's
+    first token and then replaced by the step's last rows. q_temp = (coef, every): q is multiplied by 1 + coef ln(floor((p + 1) / every) + 1)
+    at position p. v_norm: every value head is divided by its root mean square (eps inside the root). Writes q_out [T, heads * qk_dim] in
+    the activation dtype and the keys and values into the paged cache."""
+    _check("proj", proj, torch.float32)
+    P, T, R = proj.shape
+    view = kv.c_view()
+    if R != (heads + view.kv_heads) * qk_dim + view.kv_heads * v_dim:
+        raise L.KernelError(f"qkv_conv: the projection has {R} columns, expected {(heads + view.kv_heads) * qk_dim + view.kv_heads * v_dim}")
+    _check("q_out", q_out, None, (T, heads * qk_dim))
+    if bias is not None:
+        _check("bias", bias, torch.float32, (R,))
+    taps = 1
+    if conv_w is not None:
+        _check("conv_w", conv_w, torch.float32)
+        if conv_w.dim() != 2 or conv_w.shape[1] != R:
+            raise L.KernelError(f"qkv_conv: conv_w must be [taps, {R}], got {tuple(conv_w.shape)}")
+        taps = conv_w.shape[0]
+    slot_stride = 0
+    if taps > 1:
+        _check("conv_state", conv_state, torch.float32)
+        if tuple(conv_state.shape[1:]) != (taps - 1, R):
+            raise L.KernelError(f"qkv_conv: conv_state must be [slots, {taps - 1}, {R}], got {tuple(conv_state.shape)}")
+        slot_stride = conv_state.stride(0)
+        L.launches += 1
+    for name, t_, n in (("seg_of_token", seg_of_token, T), ("positions", positions, T), ("seg_start", seg_start, n_segments + 1), ("seg_slot", seg_slot, n_segments)):
+        _check(name, t_, torch.int32, (n,))
+    coef, every = (0.0, 0) if q_temp is None else (float(q_temp[0]), int(q_temp[1]))
+    L.call("ib_qkv_conv", proj.data_ptr(), P, T * R, _ptr(bias), _ptr(conv_w), taps, _ptr(conv_state) if taps > 1 else None, slot_stride, seg_of_token.data_ptr(),
+           seg_start.data_ptr(), seg_slot.data_ptr(), n_segments, positions.data_ptr(), T, heads, qk_dim, v_dim, coef, every, 1 if v_norm else 0, float(eps),
+           q_out.data_ptr(), dtype_code(q_out.dtype), C.byref(view), status.data_ptr(), _stream())
+
+
+def sigmoid_attention_mma_supports(heads: int, kv_heads: int, qk_dim: int, v_dim: int) -> bool:
+    return bool(L.load().ib_sigmoid_attention_mma_supports(int(heads), int(kv_heads), int(qk_dim), int(v_dim)))
+
+
+def sigmoid_attention(q: torch.Tensor, kv: KvLayerView, positions: torch.Tensor, seg_of_token: torch.Tensor, scale: float, r1: Optional[torch.Tensor],
+                      r2: Optional[torch.Tensor], pb: Optional[torch.Tensor], out: torch.Tensor, heads: int, qk_dim: int, v_dim: int, status: torch.Tensor,
+                      n_slices: int = 1, slice_keys: int = 1 << 30, part: Optional[torch.Tensor] = None, units: Optional[torch.Tensor] = None,
+                      tensor_cores: bool = False) -> None:
+    """out[t, h] = sum over keys j <= position of sigmoid((q . k_j) * scale - r1[h] ln(1 + r2[h] (position - j)) + pb[h]) v_j: causal attention whose
+    weights are sigmoids and are not normalised. r1, r2, pb: float32 [heads] or None. n_slices > 1: the keys are cut into slices of slice_keys whose
+    partial sums (`part`, float32, at least T * heads * n_slices * v_dim values) are added in order. tensor_cores: the m16n8k16 kernel (bfloat16; see
+    `sigmoid_attention_mma_supports`), with `units` None (a CTA per token and kv head) or int32 [n, 2] of (first token, tokens) runs of consecutive
+    tokens of one request, at most 16 // (heads // kv_heads) tokens each."""
+    T = q.shape[0]
+    view = kv.c_view()
+    _check("q", q, None, (T, heads * qk_dim))
+    _check("out", out, q.dtype, (T, heads * v_dim))
+    _check("positions", positions, torch.int32, (T,))
+    _check("seg_of_token", seg_of_token, torch.int32, (T,))
+    for name, v in (("r1", r1), ("r2", r2), ("pb", pb)):
+        if v is not None:
+            _check(name, v, torch.float32, (heads,))
+    if n_slices > 1:
+        _check("part", part, torch.float32)
+        if part.numel() < T * heads * n_slices * v_dim:
+            raise L.KernelError("sigmoid_attention: the scratch for the slices is too small")
+        L.launches += 1
+    if tensor_cores:
+        n_units = T
+        if units is not None:
+            _check("units", units, torch.int32)
+            n_units = units.shape[0]
+        L.call("ib_sigmoid_attention_mma", q.data_ptr(), C.byref(view), positions.data_ptr(), seg_of_token.data_ptr(), _ptr(units), n_units, float(scale), _ptr(r1), _ptr(r2),
+               _ptr(pb), out.data_ptr(), _ptr(part), T, heads, qk_dim, v_dim, n_slices, slice_keys, status.data_ptr(), _stream())
+        return
+    L.call("ib_sigmoid_attention", q.data_ptr(), dtype_code(q.dtype), C.byref(view), positions.data_ptr(), seg_of_token.data_ptr(), float(scale), _ptr(r1), _ptr(r2),
+           _ptr(pb), out.data_ptr(), _ptr(part), T, heads, qk_dim, v_dim, n_slices, slice_keys, status.data_ptr(), _stream())

@@ -1,2 +1,2 @@
 """Importing this package registers every architecture the engine has."""
-from . import busadra, lulenex, qwen3, zabonex  # noqa: F401
+from . import busadra, ditalorn, lulenex, qwen3, zabonex  # noqa: F401

@@ -1,2 +1,2 @@
 """Parts of a decoder. Importing the package registers the standard parts."""
-from . import base, plan, standard, latent, experts, recurrent, canon, shift, scan, parallel, loop  # noqa: F401
+from . import base, plan, standard, latent, experts, recurrent, canon, shift, scan, parallel, loop, sigmoid  # noqa: F401

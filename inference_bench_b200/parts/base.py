@@ -95,7 +95,19 @@ class Part:
         for the runtime's mode (fuse, convert, upload derived tables)."""
 
 
+@dataclass
+class NormedDelta:
+    """A contribution to the residual stream that still has to go through a norm of its own before it is added: what a block leaves for the
+    next norm when its sublayers' outputs are normed (x += norm(sum of `delta` + `bias`)). A norm that is given one as `delta` applies `norm`
+    (same kind, same epsilon) to it first; `Norm.takes_normed_delta` says whether it can."""
+    delta: torch.Tensor                     # float32 [P, T, H]
+    norm: "Norm"
+    bias: Optional[torch.Tensor] = None     # float32 [H], added to the summed partial sums before the norm
+
+
 class Norm(Part):
+    takes_normed_delta = False   # True: `forward` takes a `NormedDelta` as delta
+
     def forward(self, ctx: "StepContext", x: torch.Tensor, delta: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """x: float32 residual stream [T, H], updated in place by `delta` (float32 [P, T, H] or None);
         returns the normalised rows in the runtime's activation dtype. With `rows` only those

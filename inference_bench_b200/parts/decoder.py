@@ -29,9 +29,11 @@ class Decoder:
         for lp in plan.layers:
             if lp.block not in base.BLOCKS:
                 raise KeyError(f"no block arrangement {lp.block!r} is registered")
+            # a parameter of the arrangement that is a `PartSpec` is a norm of its own (a norm on a sublayer's output, for instance)
+            own = {k: _build(base.NORMS, "norm", v) if isinstance(v, PartSpec) else v for k, v in lp.block_params}
             self.blocks.append(base.BLOCKS[lp.block](
                 _build(base.NORMS, "norm", lp.mixer_norm), _build(base.MIXERS, "mixer", lp.mixer),
-                _build(base.NORMS, "norm", lp.feed_forward_norm), _build(base.FEED_FORWARDS, "feed-forward", lp.feed_forward), **dict(lp.block_params)))
+                _build(base.NORMS, "norm", lp.feed_forward_norm), _build(base.FEED_FORWARDS, "feed-forward", lp.feed_forward), **own))
         self.stream_parts: list[base.StreamPart] = [_build(base.STREAM_PARTS, "stream part", sp) for sp in plan.stream_parts]
         self.final_norm: base.Norm = _build(base.NORMS, "norm", plan.final_norm)
         self.head: base.Head = _build(base.HEADS, "head", plan.head)
@@ -75,6 +77,11 @@ class Decoder:
         like the reference's per-layer trace buffer (crates/specrt/src/runtime.rs:1406-1412, 2480-2504)."""
         rows = ctx.logit_rows.long()
         out = x.index_select(0, rows)
+        if isinstance(pending, base.NormedDelta):   # a contribution that goes through a norm of its own first
+            y = pending.delta.sum(0).index_select(0, rows)
+            if pending.bias is not None:
+                y = y + pending.bias
+            return out + pending.norm.w * (y * torch.rsqrt((y * y).mean(-1, keepdim=True) + pending.norm.eps))
         if pending is not None:
             for p in range(pending.shape[0]):
                 out = out + pending[p].index_select(0, rows)

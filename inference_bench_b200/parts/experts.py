@@ -5,7 +5,9 @@ plus (optionally) one shared expert that every token uses.
     largest s, the best `groups_keep` groups stay;  of their experts the `top` with the largest s are chosen;
     out = sum_e weight_e * down_e(silu(gate_e h) * up_e h)  [+ shared(h)],   weight_e = s_e * route_scale
     (with `renorm`: s_e / sum of the chosen s, times route_scale).
-`score="sigmoid"`: s_e = sigmoid of expert e's own logit instead of the softmax. `weight_on="input"`: the weight scales what the expert
+`score="sigmoid"`: s_e = sigmoid of expert e's own logit instead of the softmax. `correction` names a tensor of one number an expert
+that is added to s where groups and experts are chosen and left out of the weights; `group_top` n makes a group's score the sum of
+its n largest choice scores (experts of groups that do not stay cannot be chosen, whatever the sign of their scores). `weight_on="input"`: the weight scales what the expert
 reads, out = sum_e down_e(silu(gate_e (weight_e h)) * up_e (weight_e h)), which is not the same thing for a gated expert.
 The step's (token, expert) pairs are regrouped by expert on the device (no trip to the host, so the step can be captured),
 the experts' products run on the regrouped rows, and the weighted sum returns them to token order.
@@ -24,12 +26,15 @@ from .base import WeightSpec
 class RoutedExperts(base.FeedForward):
     def __init__(self, prefix: str, hidden: int, expert_ff: int, experts: int, top: int, route_scale: float = 1.0, groups: int = 1, groups_keep: int = 1,
                  shared_ff: int = 0, renorm: bool = False, names: tuple = ("router", "e{}", "shared", "gate", "up", "down"), score: str = "softmax",
-                 weight_on: str = "output"):
+                 weight_on: str = "output", correction: str = "", group_top: int = 1):
         if not 0 < top <= experts or experts % groups or not 0 < groups_keep <= groups:
             raise ValueError(f"top {top} of {experts} experts in {groups} groups of which {groups_keep} stay")
         if score not in ("softmax", "sigmoid") or weight_on not in ("output", "input"):
             raise ValueError(f"score {score!r} (softmax, sigmoid) or weight_on {weight_on!r} (output, input) is not known")
-        self.score, self.weight_on = score, weight_on
+        if not 1 <= group_top <= 4:
+            raise ValueError(f"a group's score is the sum of its {group_top} largest scores: 1 to 4 are built")
+        self.score, self.weight_on, self.correction, self.group_top = score, weight_on, correction, int(group_top)
+        self.w_correction = None
         self.prefix, self.hidden, self.expert_ff, self.experts, self.top = prefix, hidden, expert_ff, experts, top
         self.route_scale, self.groups, self.groups_keep, self.shared_ff, self.renorm, self.names = route_scale, groups, groups_keep, shared_ff, renorm, tuple(names)
         self.w_router = self.w_gu = self.w_d = self.shared_gu = self.shared_d = None
@@ -45,6 +50,8 @@ class RoutedExperts(base.FeedForward):
         specs = [WeightSpec(f"{self.prefix}.{self.names[0]}", (self.experts, W))]
         for k in range(self.experts):
             specs += [WeightSpec(self._expert(k, 0), (F, W)), WeightSpec(self._expert(k, 1), (F, W)), WeightSpec(self._expert(k, 2), (W, F))]
+        if self.correction:
+            specs.append(WeightSpec(f"{self.prefix}.{self.correction}", (self.experts,), std=0.1))
         if self.shared_ff:
             S = self.shared_ff
             specs += [WeightSpec(self._shared(0), (S, W)), WeightSpec(self._shared(1), (S, W)), WeightSpec(self._shared(2), (W, S))]
@@ -52,6 +59,8 @@ class RoutedExperts(base.FeedForward):
 
     def bind(self, weights, rt):
         self.w_router = rt.matrix(weights[f"{self.prefix}.{self.names[0]}"])
+        if self.correction:
+            self.w_correction = rt.vector(weights[f"{self.prefix}.{self.correction}"])
         # [experts, gate rows then up rows, width] and [experts, width, inner]: one tensor each, so a tile of the grouped product finds its expert by an offset
         self.w_gu = rt.upload(torch.stack([torch.cat([weights[self._expert(k, 0)], weights[self._expert(k, 1)]], dim=0) for k in range(self.experts)]), rt.act_dtype)
         self.w_d = rt.upload(torch.stack([weights[self._expert(k, 2)] for k in range(self.experts)]), rt.act_dtype)
@@ -64,7 +73,7 @@ class RoutedExperts(base.FeedForward):
         R = T * top
         logits = rt.linear(h, self.w_router)                     # float32 partial sums [P, T, E]
         idx, wt = rt.empty((T, top), torch.int32), rt.empty((T, top), torch.float32)
-        ops.moe_route(logits, self.groups, self.groups_keep, top, self.route_scale, self.renorm, idx, wt, self.score)
+        ops.moe_route(logits, self.groups, self.groups_keep, top, self.route_scale, self.renorm, idx, wt, self.score, correction=self.w_correction, group_top=self.group_top)
         on_input = self.weight_on == "input"
         offsets, tile_start = rt.empty((E + 1,), torch.int32), rt.empty((E + 1,), torch.int32)
         row_of_pair, token_of_row = rt.empty((R,), torch.int32), rt.empty((R,), torch.int32)

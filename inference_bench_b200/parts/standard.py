@@ -43,10 +43,25 @@ class RMSNorm(base.Norm):
         ops.norm_residual(x, delta, self.w, float(mult), self.eps, act)
         return x if act is None else act
 
+    takes_normed_delta = True
+
     def forward(self, ctx, x, delta, rows=None):
         n = x.shape[0] if rows is None else rows.shape[0]
         out = ctx.rt.empty((n, self.size))
+        if isinstance(delta, base.NormedDelta):   # the contribution goes through its own norm on its way into the stream: one kernel for both norms
+            post = delta.norm
+            if not isinstance(post, RMSNorm) or post.eps != self.eps:
+                raise ValueError("a contribution's own norm must be an RMS norm with this norm's epsilon")
+            ops.post_norm(x, delta.delta, delta.bias, post.w, self.w, out, self.eps, rows)
+            return out
         ops.add_rmsnorm(x, delta, self.w, out, self.eps, rows)
+        return out
+
+    def add_post(self, ctx, x, delta, bias, next_norm: Optional["RMSNorm"] = None):
+        """This norm on a sublayer's output: x += w * rms_unit(sum of `delta` + bias), in place; with `next_norm`, returns that norm of the
+        updated stream in the activation dtype (the next sublayer's input), from the same kernel."""
+        out = None if next_norm is None else ctx.rt.empty((x.shape[0], self.size))
+        ops.post_norm(x, delta, bias, self.w, None if next_norm is None else next_norm.w, out, self.eps)
         return out
 
 
@@ -316,19 +331,34 @@ class DenseXielu(base.FeedForward):
 class TokenEmbedding(base.Embedding):
     """x[t] = float32(E[token_t]) * 1 (crates/kir/src/prims.rs:387)."""
 
-    def __init__(self, name: str, vocab: int, hidden: int):
-        self.name, self.vocab, self.hidden = name, vocab, hidden
-        self.table = None
+    def __init__(self, name: str, vocab: int, hidden: int, scale: float = 1.0, positions: Optional[str] = None, max_positions: int = 0):
+        """scale: a constant on the token's vector. positions: the name of a table [max_positions, hidden] of learned vectors, one a position,
+        added to it unscaled: x[t] = E[token_t] * scale + P[position_t]."""
+        if positions is not None and max_positions <= 0:
+            raise ValueError("a table of learned positions needs its number of positions")
+        self.name, self.vocab, self.hidden, self.scale, self.positions, self.max_positions = name, vocab, hidden, float(scale), positions, max_positions
+        self.table = self.pos_table = None
 
     def weight_specs(self):
-        return [WeightSpec(self.name, (self.vocab, self.hidden))]
+        specs = [WeightSpec(self.name, (self.vocab, self.hidden))]
+        if self.positions is not None:
+            specs.append(WeightSpec(self.positions, (self.max_positions, self.hidden)))
+        return specs
 
     def bind(self, weights, rt):
         self.table = rt.matrix(weights[self.name])
+        if self.positions is not None:
+            self.pos_table = rt.matrix(weights[self.positions])
 
     def forward(self, ctx):
         x = ctx.rt.empty((ctx.n_tokens, self.hidden), torch.float32)
-        ops.embed(self.table.weight, ctx.token_ids, x, ctx.rt.status)
+        if self.pos_table is None and self.scale == 1.0:
+            ops.embed(self.table.weight, ctx.token_ids, x, ctx.rt.status)
+        elif self.pos_table is None:
+            ops.embed(self.table.weight, ctx.token_ids, x, ctx.rt.status)
+            ops.scale_values(x, self.scale)
+        else:
+            ops.embed_pos(self.table.weight, ctx.token_ids, self.pos_table.weight, ctx.positions, self.scale, x, ctx.rt.status)
         return x
 
 
@@ -406,6 +436,38 @@ class OutNormBlock(base.Block):
             h = self.feed_forward_norm.add_normed(ctx, x, f, self.residual_mult)
         ctx.memo[key] = h
         return None
+
+
+@base.register_block("sandwich")
+class SandwichBlock(base.Block):
+    """x += post1(mixer(norm1(x))); x += post2(feed_forward(norm2(x))): a norm in front of every sublayer and another on what it gives back.
+    The two output norms are the arrangement's own parts (`post_norms`: two `PartSpec`-built norms handed in by the plan as parameters).
+    Each output norm runs in the kernel of the input norm that follows it: post1 with norm2, post2 with the next block's norm1 (or the final
+    norm), to which the feed-forward's contribution goes as a `NormedDelta`. A mixer's output bias is added before post1. A layer without a
+    feed-forward has the first half only."""
+
+    takes_out_bias = True
+
+    def __init__(self, mixer_norm, mixer, feed_forward_norm, feed_forward, post_mixer_norm=None, post_feed_forward_norm=None):
+        base.Block.__init__(self, mixer_norm, mixer, feed_forward_norm, feed_forward)
+        self.has_ff = not isinstance(feed_forward, NoFeedForward)
+        norms = [mixer_norm, post_mixer_norm] + ([feed_forward_norm, post_feed_forward_norm] if self.has_ff else [])
+        if any(not isinstance(n, RMSNorm) for n in norms) or len({n.eps for n in norms}) != 1:
+            raise ValueError("this arrangement is built for four RMS norms with one epsilon")
+        self.post_mixer_norm, self.post_feed_forward_norm = post_mixer_norm, post_feed_forward_norm
+
+    def parts(self):
+        return [*base.Block.parts(self), self.post_mixer_norm] + ([self.post_feed_forward_norm] if self.has_ff else [])
+
+    def forward(self, ctx, x, pending, cache):
+        if pending is not None and not isinstance(pending, base.NormedDelta):
+            raise RuntimeError("this block follows a block that left a plain contribution to add: mixing arrangements is not supported")
+        h = self.mixer_norm.forward(ctx, x, pending)
+        a = self.mixer.forward(ctx, h, cache)
+        if not self.has_ff:
+            return base.NormedDelta(a, self.post_mixer_norm, self.mixer.out_bias)
+        h = self.post_mixer_norm.add_post(ctx, x, a, self.mixer.out_bias, self.feed_forward_norm)
+        return base.NormedDelta(self.feed_forward.forward(ctx, h), self.post_feed_forward_norm)
 
 
 @base.register_feed_forward("none")
