@@ -53,10 +53,20 @@ def causal_conv(u, taps_w):
 
 def embed(tokens, cfg, w):
     T = len(tokens)
-    return d(w["embed"])[torch.tensor(tokens, dtype=torch.long)] * float(cfg["embedding"]["scale"]) + d(w["pos"])[:T]
+    return d(w["embed"])[torch.tensor(tokens, dtype=torch.long)] * float((cfg.get("embedding") or {}).get("scale", 1.0)) + d(w["pos"])[:T]
 
 
 # ------------------------------------------------------------------------------------------ latent attention with a window
+def windowed_softmax(q, k, v, scale, window):
+    """q, k [T, H, dim], v [T, H, vdim]: position i sees j with 0 <= i - j < window (window None: every j <= i); softmax over those."""
+    T = q.shape[0]
+    s = torch.einsum("ihd,jhd->hij", q, k) * scale
+    dist = torch.arange(T).view(T, 1) - torch.arange(T).view(1, T)
+    seen = (dist >= 0) if window is None else (dist >= 0) & (dist < window)
+    a = torch.softmax(s.masked_fill(~seen, -math.inf), dim=-1)
+    return torch.einsum("hij,jhv->ihv", a, v)
+
+
 def latent_attention(h, m, w, p, eps):
     """Queries through a normed latent; keys and values of every head as maps of one normed latent a token; a position sees itself
     and the mask.size - 1 positions before it; softmax; every head's output times the sigmoid of its gate."""
@@ -67,14 +77,8 @@ def latent_attention(h, m, w, p, eps):
     c = norm_plain(h @ d(w[p + ".dkv"]).T, w[p + ".dkv.norm"], eps)
     k = (c @ d(w[p + ".uk"]).T).view(T, H, dim)
     v = (c @ d(w[p + ".uv"]).T).view(T, H, vdim)
-    s = torch.einsum("ihd,jhd->hij", q, k) * float(m["scale"])
-    i = torch.arange(T).view(T, 1)
-    j = torch.arange(T).view(1, T)
-    dist = i - j
-    seen = (dist >= 0) & (dist < int(m["mask"]["size"]))
-    s = s.masked_fill(~seen, -math.inf)
-    a = torch.softmax(s, dim=-1)
-    o = torch.einsum("hij,jhv->ihv", a, v)
+    mask = m.get("mask") or {}
+    o = windowed_softmax(q, k, v, float(m["scale"]), None if mask.get("size") is None else int(mask["size"]))
     gate = torch.sigmoid(h @ d(w[p + ".g"]).T)             # [T, H]
     o = o * gate.unsqueeze(-1)
     return o.reshape(T, H * vdim) @ d(w[p + ".o"]).T
@@ -95,26 +99,37 @@ def distance_bias(T, r1, r2):
     return d(r1).view(-1, 1, 1) * torch.log1p(d(r2).view(-1, 1, 1) * dist)
 
 
+def sigmoid_weights(q, k, v, scale, r1, r2, pb):
+    """q [T, H, dim], k [T, G, dim], v [T, G, vdim] -> [T, H, vdim]: o_i = sum_{j <= i} sigmoid(q_i . k_j * scale - bias(i - j) + pb) v_j."""
+    T, H = q.shape[0], q.shape[1]
+    rep = H // k.shape[1]
+    k, v = k.repeat_interleave(rep, dim=1), v.repeat_interleave(rep, dim=1)
+    s = torch.einsum("ihd,jhd->hij", q, k) * scale
+    if r1 is not None:
+        s = s - distance_bias(T, r1, r2)
+    if pb is not None:
+        s = s + d(pb).view(H, 1, 1)
+    a = torch.sigmoid(s) * torch.tril(torch.ones((T, T), dtype=F64))
+    return torch.einsum("hij,jhv->ihv", a, v)
+
+
 def sigmoid_attention(h, m, w, p, eps):
     """Grouped heads; biased projections; a short causal convolution on every channel of q, k, v; q times a temperature of its
     position; values divided by their root mean square per head; score minus a bias that grows with the distance; the weight of
     a key is the sigmoid of its score plus a number per head, and weights are not normalised."""
     T = h.shape[0]
-    H, G, dim, vdim = int(m["heads"]), int(m.get("kv_heads") or m["heads"]), int(m["dim"]), int(m["vdim"])
+    H, G, dim, vdim = int(m["heads"]), int(m.get("kv_heads") or m["heads"]), int(m["dim"]), int(m.get("vdim") or m["dim"])
 
     def proj(name):
-        return causal_conv(h @ d(w[f"{p}.{name}"]).T + d(w[f"{p}.{name}.b"]), w[f"{p}.{name}.conv"])
+        u = h @ d(w[f"{p}.{name}"]).T + d(w[f"{p}.{name}.b"])
+        return causal_conv(u, w[f"{p}.{name}.conv"]) if m.get("conv") else u
 
-    q = proj("q").view(T, H, dim) * query_temperature(T, m["q_temp"]).view(T, 1, 1)
+    q = proj("q").view(T, H, dim)
+    if m.get("q_temp"):
+        q = q * query_temperature(T, m["q_temp"]).view(T, 1, 1)
     k = proj("k").view(T, G, dim)
     v = rms_unit(proj("v").view(T, G, vdim), eps)
-    rep = H // G
-    k = k.repeat_interleave(rep, dim=1)
-    v = v.repeat_interleave(rep, dim=1)
-    s = torch.einsum("ihd,jhd->hij", q, k) * float(m["scale"]) - distance_bias(T, w[p + ".r1"], w[p + ".r2"])
-    a = torch.sigmoid(s + d(w[p + ".pb"]).view(H, 1, 1))
-    a = a * torch.tril(torch.ones((T, T), dtype=F64))
-    o = torch.einsum("hij,jhv->ihv", a, v)
+    o = sigmoid_weights(q, k, v, float(m["scale"]), w[p + ".r1"], w[p + ".r2"], w[p + ".pb"])
     return o.reshape(T, H * vdim) @ d(w[p + ".o"]).T + d(w[p + ".o.b"])
 
 
@@ -123,11 +138,14 @@ def route(h, f, w, p):
     """(chosen experts [T, top], their weights [T, top]). Choice scores are sigmoid(logit) + correction; a group's score is the sum of its
     two largest choice scores; only the experts of the best groups.keep groups can be chosen; the weights are the plain sigmoids."""
     r = f["router"]
-    E, top = int(r["experts"]), int(r["top"])
-    n_groups, keep = int(r["groups"]["count"]), int(r["groups"]["keep"])
-    s = torch.sigmoid(h @ d(w[p + ".router"]).T)
-    choice = s + d(w[p + ".correction"])
-    T = h.shape[0]
+    g = r.get("groups") or {}
+    return choose(torch.sigmoid(h @ d(w[p + ".router"]).T), d(w[p + ".correction"]), int(r["top"]), int(g.get("count") or 1), int(g.get("keep") or g.get("count") or 1))
+
+
+def choose(s, correction, top, n_groups, keep):
+    """s [T, E] scores in (0, 1) -> (chosen experts [T, top], their weights [T, top])."""
+    T, E = s.shape
+    choice = s + correction
     per = E // n_groups
     grouped = choice.view(T, n_groups, per)
     gscore = grouped.topk(min(2, per), dim=-1).values.sum(-1)
@@ -175,3 +193,11 @@ def hidden_states(tokens, cfg, w):
 def logits(tokens, cfg, w):
     x = hidden_states(tokens, cfg, w)[-1]
     return norm_offset(x, w["final.norm"], float(cfg["norm"]["eps"])) @ d(w["embed"]).T
+
+
+def greedy(prompt, n, cfg, w):
+    """n tokens, each the largest logit after everything before it (the lowest id on a tie)."""
+    toks = list(prompt)
+    for _ in range(n):
+        toks.append(int(torch.argmax(logits(toks, cfg, w)[-1])))
+    return toks[len(prompt):]

@@ -1,0 +1,565 @@
+"""Ditalorn in the engine against the plain implementation: each mechanism's kernels alone (with weights or inputs made so that a key just
+inside or just outside a window, a far key, a lost state row or a wrong choice of experts shows), then whole models under every way of
+cutting the work (in true 32-bit and in bfloat16), pages and slots that are used again, and greedy generation through the engine's entry
+point and scheduler."""
+from __future__ import annotations
+
+import copy
+import json
+import math
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_ditalorn as P
+import tiny_ditalorn as td
+import traces
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+TOLERANCE = {"float32": 1e-4, "bfloat16": 6e-2}   # of the largest |logit| of the sequence
+# In bfloat16 a router's choice between two experts whose choice scores are alike can go to the other one after rounding. That token's logits
+# then move by far more than rounding moves them, and through the attention over all earlier keys later tokens move a little too. With random
+# weights and three or four routed layers several rows in a hundred have such a call, so whole models are compared statistically in bfloat16:
+# the median row well inside the bound, few rows beyond it, none wildly off. What must be exact (windows, state, pages, slots, cuts) is
+# checked in float32, where no row may differ.
+BF16_ROWS_OVER = 0.12
+BF16_MEDIAN = 1.5e-2
+BF16_WORST = 1.5
+
+
+@pytest.fixture(scope="module")
+def rt16():
+    from inference_bench_b200.engine.runtime import Runtime
+    return Runtime(DEV, dtype="bfloat16")
+
+
+@pytest.fixture(scope="module")
+def rt32():
+    from inference_bench_b200.engine.runtime import Runtime
+    return Runtime(DEV, dtype="float32")
+
+
+@pytest.fixture(scope="module")
+def ddirs(tmp_path_factory):
+    root = tmp_path_factory.mktemp("ditalorn")
+    return {name: td.write_model(name, root / name) for name in td.CONFIGS}
+
+
+def _weights(name):
+    c = td.CONFIGS[name]
+    return c["config"], td.tensors(c["config"], c["seed"])
+
+
+def _f32(t):
+    return t.to(DEV, torch.float32).contiguous()
+
+
+def _ctx(rt, runs, slots=None):
+    """A step's context for segments given as (first position, tokens)."""
+    from inference_bench_b200.engine.context import Segment, build_context
+    return build_context(rt, [Segment(i, (slots[i] if slots else i), p0, [0] * n, []) for i, (p0, n) in enumerate(runs)])
+
+
+def _paged(rows_by_plane, page, dtype, g, entry=1, entries=2, spare=3):
+    """A pool [entries, pages, planes, heads, page, width] whose entry `entry` holds the given rows ([n, heads, width] a plane) on shuffled
+    pages, and the page order."""
+    n, heads, width = rows_by_plane[0].shape
+    n_pages = -(-n // page)
+    perm = torch.randperm(n_pages + spare, generator=g)[:n_pages]
+    pool = torch.zeros((entries, n_pages + spare, len(rows_by_plane), heads, page, width), dtype=dtype, device=DEV)
+    for pl, rows in enumerate(rows_by_plane):
+        for j in range(n):
+            pool[entry, perm[j // page], pl, :, j % page] = rows[j].to(dtype)
+    return pool, perm
+
+
+# ------------------------------------------------------------------------------------------ the router's choice
+@pytest.mark.parametrize("E,groups,keep,top", [(6, 3, 2, 2), (8, 2, 1, 3), (16, 4, 2, 4), (7, 1, 1, 1), (12, 12, 5, 5), (64, 8, 3, 6), (4, 2, 2, 4)])
+def test_choice_of_experts_with_a_correction_and_group_sums(rt32, E, groups, keep, top):
+    """Sigmoid scores plus a correction choose groups (by the sum of their two largest choice scores) and experts; the weights leave the correction
+    out. Corrections are large enough that whole groups have negative choice scores, also kept ones."""
+    from inference_bench_b200.kernels import ops
+    g = torch.Generator().manual_seed(E * 31 + top)
+    T = 300
+    logits = torch.randn((2, T, E), generator=g) * 1.5
+    corr = torch.randn((E,), generator=g) * 0.8 - 0.6
+    idx = torch.empty((T, top), dtype=torch.int32, device=DEV)
+    wt = torch.empty((T, top), dtype=torch.float32, device=DEV)
+    ops.moe_route(_f32(logits), groups, keep, top, 1.0, False, idx, wt, "sigmoid", correction=_f32(corr), group_top=2)
+    s = torch.sigmoid(logits.double().sum(0))
+    widx, wwt = P.choose(s, corr.double(), top, groups, keep)
+    got = idx.cpu().long()
+    # a close call between two choice scores may fall either way in 32-bit: compare where the plain choice is clear
+    choice = s + corr.double()
+    order = torch.sort(choice, dim=-1, descending=True).values
+    clear = torch.ones(T, dtype=torch.bool)
+    per = E // groups
+    gs = choice.view(T, groups, per).topk(min(2, per), -1).values.sum(-1).sort(-1, descending=True).values
+    if keep < groups:
+        clear &= (gs[:, keep - 1] - gs[:, keep]) > 1e-5
+    assert clear.float().mean() > 0.95
+    for t in torch.nonzero(clear).flatten().tolist():
+        if sorted(got[t].tolist()) != sorted(widx[t].tolist()):
+            kept = torch.sort(choice[t][widx[t]]).values
+            assert (order[t][:-1] - order[t][1:]).abs().min() < 1e-5, f"token {t}: chose {got[t].tolist()}, plain {widx[t].tolist()}"
+            continue
+        pairs = dict(zip(got[t].tolist(), wt[t].cpu().tolist()))
+        for e, a in zip(widx[t].tolist(), wwt[t].tolist()):
+            assert abs(pairs[e] - a) < 1e-6
+
+
+# ------------------------------------------------------------------------------------------ norms around the sublayers, embedding with positions
+@pytest.mark.parametrize("H", [48, 132, 1024, 4100])
+def test_output_norm_with_the_next_input_norm_and_embedding_with_positions(rt32, rt16, H):
+    from inference_bench_b200.kernels import ops
+    g = torch.Generator().manual_seed(H)
+    T, eps = 37, 1e-5
+    x, delta, bias = torch.randn((T, H), generator=g) * 2, torch.randn((3, T, H), generator=g), torch.randn((H,), generator=g)
+    w_post, w_next = 1 + 0.3 * torch.randn((H,), generator=g), 1 + 0.3 * torch.randn((H,), generator=g)
+    y = delta.double().sum(0) + bias.double()
+    want_x = x.double() + w_post.double() * P.rms_unit(y, eps)
+    want_h = w_next.double() * P.rms_unit(want_x, eps)
+    xd, out = _f32(x), torch.empty((T, H), dtype=torch.float32, device=DEV)
+    ops.post_norm(xd, _f32(delta), _f32(bias), _f32(w_post), _f32(w_next), out, eps)
+    assert (xd.cpu().double() - want_x).abs().max() < 2e-5 and (out.cpu().double() - want_h).abs().max() < 2e-5
+    # the add alone; then gathered rows in bfloat16 that leave the stream as it is
+    xd2 = _f32(x)
+    ops.post_norm(xd2, _f32(delta), _f32(bias), _f32(w_post), None, None, eps)
+    assert torch.equal(xd2, xd)
+    rows = torch.tensor([5, 0, 36, 5], dtype=torch.int32, device=DEV)
+    xd3, out16 = _f32(x), torch.empty((4, H), dtype=torch.bfloat16, device=DEV)
+    ops.post_norm(xd3, _f32(delta), None, _f32(w_post), _f32(w_next), out16, eps, rows=rows)
+    assert torch.equal(xd3.cpu(), x)
+    y2 = delta.double().sum(0)
+    want2 = w_next.double() * P.rms_unit(x.double() + w_post.double() * P.rms_unit(y2, eps), eps)
+    assert (out16.float().cpu().double() - want2[rows.cpu().long()]).abs().max() < 3e-2
+    # without a contribution: the input norm alone
+    ops.post_norm(xd3, None, None, None, _f32(w_next), out, eps)
+    assert (out.cpu().double() - w_next.double() * P.rms_unit(x.double(), eps)).abs().max() < 2e-5
+    # the embedding
+    V, n_pos, scale = 50, 64, 7.5
+    table, pos = torch.randn((V, H), generator=g).to(torch.bfloat16), torch.randn((n_pos, H), generator=g).to(torch.bfloat16)
+    toks = torch.randint(0, V, (T,), generator=g).to(torch.int32)
+    places = torch.randint(0, n_pos, (T,), generator=g).to(torch.int32)
+    e = torch.empty((T, H), dtype=torch.float32, device=DEV)
+    ops.embed_pos(table.to(DEV), toks.to(DEV), pos.to(DEV), places.to(DEV), scale, e, rt16.status)
+    want = table.double()[toks.long()] * scale + pos.double()[places.long()]
+    assert (e.cpu().double() - want).abs().max() < 1e-5
+    rt16.check_status()
+
+
+# ------------------------------------------------------------------------------------------ latent attention with a window
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,rank,page,window", [(6, 64, 16, 40), (3, 32, 16, 9), (5, 24, 8, 1), (8, 128, 32, 48), (4, 64, 64, 17), (2, 16, 16, 1000),
+                                                     (20, 48, 16, 33), (1, 256, 16, 64)])
+def test_latent_attention_window_edges_in_portions_and_decoding(rt32, rt16, dtype, heads, rank, page, window):
+    """Prompt portions that cross page borders and span more than a window, the first tokens of a sequence, and single decoded tokens (also cut
+    into slices), all of one request on shuffled pages. One key stands out for one query: the oldest key inside the query's window and the one just
+    outside it, a query's own position, the first position. bfloat16 rows that are multiples of 16 run on the tensor-core kernel."""
+    from inference_bench_b200.kernels import ops
+    from inference_bench_b200.kernels.ops import KvLayerView
+    rt = rt32 if dtype == torch.float32 else rt16
+    n_ctx, scale = 300, 0.3
+    g = torch.Generator().manual_seed(heads * rank + page + window)
+    c = torch.randn((n_ctx, 1, rank), generator=g)
+    q = torch.randn((n_ctx, heads, rank), generator=g) * 0.3
+    needles = [(200, 200 - window + 1, 0), (201, 201 - window, 1 % heads), (150, 150, 0), (151, 0, 1 % heads), (290, 290 - window + 1, 0), (291, 291 - window, 0),
+               (3, 0, 0), (2 * page, 2 * page - 1, 1 % heads), (5, 5 - window + 1, 0), (6, 6 - window, 0)]
+    for i, (qp, key, head) in enumerate(needles):
+        if not (0 <= key < n_ctx and 0 <= qp < n_ctx) or key > qp:
+            continue
+        col = (i * 5) % rank
+        c[key, 0, col] = 6.0
+        q[qp, head, col] = 25.0
+    c, q = c.to(dtype).float(), q.to(dtype).float()
+    want = P.windowed_softmax(q.double(), c.double().expand(n_ctx, heads, rank), c.double().expand(n_ctx, heads, rank), scale, window)
+    pool, perm = _paged([c], page, dtype, g)
+    tc = dtype == torch.bfloat16 and ops.latent_attention_mma_supports(rank, rank)
+    cover = -(-min(window, 292) // 64)      # slices of 64 keys that cover what the longest-seeing token of the second step sees
+    for runs, slices in (([(100, 120), (0, 7), (290, 1), (291, 1), (2 * page - 2, 4), (230, 45)], (1, 1 << 30)), ([(290, 1), (291, 1), (5, 1), (6, 1), (150, 1)], (cover + 1, 64)),
+                         ([(200, 1), (201, 1), (0, 1)], (1, 1 << 30))):
+        positions = [p0 + i for p0, n in runs for i in range(n)]
+        T = len(positions)
+        ctx = _ctx(rt, runs)
+        table = perm.to(torch.int32).reshape(1, -1).repeat(len(runs), 1).contiguous().to(DEV)
+        view = KvLayerView(pool, 1, table)
+        qd = _f32(q[positions])
+        out = torch.empty((T, heads, rank), dtype=dtype, device=DEV)
+        n_slices, slice_keys = slices
+        scratch = (torch.empty((T * heads * n_slices * rank,), dtype=torch.float32, device=DEV), torch.empty((T * heads * n_slices * 2,), dtype=torch.float32, device=DEV))
+        if tc:
+            rows = ops.latent_attention_mma_rows(rank, rank, heads * max(n for _, n in runs))
+            per = rows // heads
+            units = None
+            if per > 1 and max(n for _, n in runs) > 1:
+                u, t0 = [], 0
+                for _, n in runs:
+                    u += [(t, min(per, t0 + n - t)) for t in range(t0, t0 + n, per)]
+                    t0 += n
+                units = torch.tensor(u, dtype=torch.int32, device=DEV)
+            ops.latent_attention_mma(qd, view, ctx.positions, ctx.seg_of_token, units, scale, out, rank, n_slices, slice_keys, scratch, rt.status, rows, window=window)
+        else:
+            ops.latent_attention(qd, view, ctx.positions, ctx.seg_of_token, scale, out, rank, n_slices, slice_keys, scratch, rt.status, window=window)
+        got = out.float().cpu().double()
+        tol = 3e-5 if dtype == torch.float32 else 4e-2
+        err = (got - want[positions]).abs().amax(dim=(1, 2))
+        assert err.max().item() < tol, f"positions {[positions[i] for i in torch.nonzero(err >= tol).flatten().tolist()]} differ by up to {err.max().item():.2e}"
+    rt.check_status()
+
+
+# ------------------------------------------------------------------------------------------ attention with sigmoid weights
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,page", [(4, 1, 64, 80, 16), (4, 2, 32, 16, 16), (5, 5, 24, 40, 8), (8, 2, 64, 128, 32), (16, 1, 32, 32, 64), (3, 1, 40, 24, 16),
+                                                          (6, 2, 128, 64, 16), (32, 1, 16, 16, 16)])
+def test_sigmoid_attention_far_keys_and_the_causal_edge(rt32, rt16, dtype, heads, kv_heads, dim, vdim, page):
+    """Weights that are not normalised: a key far back that stands out adds its value with a weight near one whatever lies between, the key right
+    after a query's position adds nothing, the distance bias and the bias per head move every weight. Prompt portions and single tokens cut into
+    slices, on shuffled pages. bfloat16 sizes that are multiples of 16 with up to 16 heads a kv head run on the tensor-core kernel."""
+    from inference_bench_b200.kernels import ops
+    from inference_bench_b200.kernels.ops import KvLayerView
+    rt = rt32 if dtype == torch.float32 else rt16
+    n_ctx, scale = 330, 0.25
+    g = torch.Generator().manual_seed(heads * dim + vdim + page)
+    k, v = torch.randn((n_ctx, kv_heads, dim), generator=g), torch.randn((n_ctx, kv_heads, vdim), generator=g)
+    q = torch.randn((n_ctx, heads, dim), generator=g) * 0.5
+    r1, r2, pb = 0.1 + torch.rand((heads,), generator=g), 0.1 + torch.rand((heads,), generator=g), torch.randn((heads,), generator=g) - 3.0
+    group = heads // kv_heads
+    for i, (qp, key, head) in enumerate([(320, 3, 0), (321, 322, 1 % heads), (200, 200, 0), (150, 149, heads - 1), (2 * page, 2 * page - 1, 0), (300, 0, heads - 1)]):
+        if key >= n_ctx:
+            continue
+        col = (i * 7) % dim
+        k[key, head // group, col] = 6.0
+        q[qp, head, col] = 25.0
+    k, v, q = k.to(dtype).float(), v.to(dtype).float(), q.to(dtype).float()
+    want = P.sigmoid_weights(q.double(), k.double(), v.double(), scale, r1, r2, pb)
+    width = max(dim, vdim)
+    pad = lambda t: torch.cat([t, torch.zeros((*t.shape[:2], width - t.shape[2]))], dim=2)
+    pool, perm = _paged([pad(k), pad(v)], page, dtype, g)
+    tc = dtype == torch.bfloat16 and ops.sigmoid_attention_mma_supports(heads, kv_heads, dim, vdim)
+    for runs, slices in (([(100, 130), (0, 7), (320, 1), (321, 1), (2 * page - 2, 4), (280, 40)], (1, 1 << 30)), ([(320, 1), (300, 1), (0, 1), (150, 1)], (4, 128)),
+                         ([(200, 1), (2 * page, 1)], (1, 1 << 30))):
+        positions = [p0 + i for p0, n in runs for i in range(n)]
+        T = len(positions)
+        ctx = _ctx(rt, runs)
+        table = perm.to(torch.int32).reshape(1, -1).repeat(len(runs), 1).contiguous().to(DEV)
+        view = KvLayerView(pool, 1, table)
+        qd = q[positions].reshape(T, heads * dim).to(DEV, dtype).contiguous()
+        out = torch.empty((T, heads * vdim), dtype=dtype, device=DEV)
+        n_slices, slice_keys = slices
+        part = torch.empty((T * heads * n_slices * vdim,), dtype=torch.float32, device=DEV)
+        units = None
+        per = 16 // group if tc else 1
+        if per > 1 and max(n for _, n in runs) > 1:
+            u, t0 = [], 0
+            for _, n in runs:
+                u += [(t, min(per, t0 + n - t)) for t in range(t0, t0 + n, per)]
+                t0 += n
+            units = torch.tensor(u, dtype=torch.int32, device=DEV)
+        ops.sigmoid_attention(qd, view, ctx.positions, ctx.seg_of_token, scale, _f32(r1), _f32(r2), _f32(pb), out, heads, dim, vdim, rt.status, n_slices=n_slices,
+                              slice_keys=slice_keys, part=part, units=units, tensor_cores=tc)
+        got = out.float().cpu().double().view(T, heads, vdim)
+        ref = want[positions]
+        tol = 5e-5 if dtype == torch.float32 else 2e-2
+        err = (got - ref).abs().amax(dim=(1, 2)) / max(1.0, ref.abs().max().item())
+        assert err.max().item() < tol, f"positions {[positions[i] for i in torch.nonzero(err >= tol).flatten().tolist()]} differ by up to {err.max().item():.2e}"
+    rt.check_status()
+
+
+# ------------------------------------------------------------------------------------------ the convolution of q, k, v with its state, temperature, value norm
+PLAN = [[("a", 1), ("b", 2)], [("a", 1), ("b", 1)], [("a", 2)], [("a", 7), ("b", 6)], [("c", 1), ("a", 3)], [("c", 2), ("a", 9)], [("c", 11)], [("c", 1)], [("c", 1)]]
+LENS = {"a": 23, "b": 9, "c": 16}     # b ends after the fourth step; c takes its slot, zeroed
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,taps,every", [(4, 1, 64, 80, 3, 4), (4, 2, 32, 16, 4, 5), (5, 5, 24, 40, 1, 0), (2, 1, 16, 48, 2, 1), (3, 1, 40, 24, 6, 7)])
+def test_convolution_of_projections_over_portions_and_slots(rt32, rt16, dtype, heads, kv_heads, dim, vdim, taps, every):
+    """Three requests in two slots (the third uses the second's again), portions of 1, 2 and more tokens beside one another: every row of q and
+    every cached k and v equals the plain convolution of the whole sequence, with the temperature and the value norm."""
+    from inference_bench_b200.kernels import ops
+    from inference_bench_b200.kernels.ops import KvLayerView
+    rt = rt32 if dtype == torch.float32 else rt16
+    g = torch.Generator().manual_seed(heads * dim + taps)
+    R = (heads + kv_heads) * dim + kv_heads * vdim
+    eps, coef, page = 1e-5, 0.8, 8
+    u = {r: torch.randn((2, n, R), generator=g) for r, n in LENS.items()}
+    bias, conv = torch.randn((R,), generator=g) * 0.3, torch.randn((R, taps), generator=g) * 0.5
+    want = {}
+    for r, n in LENS.items():
+        y = P.causal_conv(u[r].double().sum(0) + bias.double(), conv)
+        qq = y[:, :heads * dim].view(n, heads, dim)
+        if every:
+            qq = qq * P.query_temperature(n, {"coef": coef, "every": every}).view(n, 1, 1)
+        kk = y[:, heads * dim:(heads + kv_heads) * dim].view(n, kv_heads, dim)
+        vv = P.rms_unit(y[:, (heads + kv_heads) * dim:].view(n, kv_heads, vdim), eps)
+        want[r] = (qq, kk, vv)
+    width = max(dim, vdim)
+    n_pages = 8
+    pool = torch.zeros((1, n_pages + 1, 2, kv_heads, page, width), dtype=dtype, device=DEV)
+    pages = {"a": [5, 2, 7], "b": [0, 3], "c": [3, 0]}          # c takes b's pages again, in another order
+    state = torch.randn((3, max(taps - 1, 1), R), generator=g).to(DEV) if taps > 1 else None   # what a slot held before is never seen: admission zeroes it
+    if state is not None:
+        state[0].zero_(), state[1].zero_()
+    slot, at = {"a": 0, "b": 1, "c": 1}, {r: 0 for r in LENS}
+    tol = 2e-5 if dtype == torch.float32 else 3e-2
+    for step in PLAN:
+        if step[0][0] == "c" and at["c"] == 0 and state is not None:
+            state[1].zero_()
+        ctx = _ctx(rt, [(at[r], n) for r, n in step], [slot[r] for r, _ in step])
+        T = sum(n for _, n in step)
+        proj = torch.cat([u[r][:, at[r]:at[r] + n] for r, n in step], dim=1).contiguous().to(DEV)
+        table = torch.full((len(step), 4), -1, dtype=torch.int32)
+        for i, (r, _) in enumerate(step):
+            table[i, :len(pages[r])] = torch.tensor(pages[r], dtype=torch.int32)
+        view = KvLayerView(pool, 0, table.to(DEV))
+        q_out = torch.empty((T, heads * dim), dtype=dtype, device=DEV)
+        ops.qkv_conv(proj, _f32(bias), _f32(conv.t()), state, ctx.seg_of_token, ctx.seg_start, ctx.seg_slot, len(step), ctx.positions, q_out, view, heads, dim, vdim, rt.status,
+                     q_temp=(coef, every) if every else None, v_norm=True, eps=eps)
+        t0 = 0
+        for r, n in step:
+            got_q = q_out[t0:t0 + n].float().cpu().double().view(n, heads, dim)
+            assert (got_q - want[r][0][at[r]:at[r] + n]).abs().max() < tol * max(1.0, want[r][0].abs().max().item()), f"q of {r} at {at[r]}"
+            for i in range(n):
+                p = at[r] + i
+                row = pool[0, pages[r][p // page], :, :, p % page].float().cpu().double()
+                assert (row[0, :, :dim] - want[r][1][p]).abs().max() < tol * max(1.0, want[r][1].abs().max().item()), f"k of {r} at {p}"
+                assert (row[1, :, :vdim] - want[r][2][p]).abs().max() < tol * 4, f"v of {r} at {p}"
+            t0 += n
+            at[r] += n
+    assert at == LENS
+    rt.check_status()
+
+
+# ------------------------------------------------------------------------------------------ whole models
+def _requests(name):
+    vocab = td.CONFIGS[name]["config"]["vocab"]
+    return {r: traces.prompt(400 + i, n, vocab) for i, (r, n) in enumerate({"a": 150, "b": 1, "c": 23, "d": 64, "e": 97, "f": 2}.items())}
+
+
+@pytest.fixture(scope="module")
+def plain_logits():
+    out = {}
+    for name in td.CONFIGS:
+        cfg, w = _weights(name)
+        out[name] = {r: P.logits(t, cfg, w).numpy() for r, t in _requests(name).items()}
+    return out
+
+
+def _runner(model_dir, dtype, max_tokens, page_size, **kw):
+    from inference_bench_b200.trace import build_runner
+    return build_runner(model_dir, dtype, max_tokens, page_size=page_size, **kw)
+
+
+def _compare(got, want_by_req, dtype, what):
+    errs, over = [], 0
+    for (r, pos), row in got.items():
+        want = want_by_req[r][pos]
+        err = np.abs(row - want).max() / np.abs(want_by_req[r]).max()
+        if dtype == "bfloat16" and TOLERANCE[dtype] < err <= BF16_WORST:
+            over += 1
+        else:
+            assert err <= TOLERANCE[dtype], f"{what}: request {r} position {pos}: |diff| = {err:.3e} of max|logit| (allowed {TOLERANCE[dtype]:.0e})"
+        errs.append(err)
+    assert len(got) == sum(len(v) for v in want_by_req.values())
+    allowed = max(BF16_ROWS_OVER * len(got), 3) if dtype == "bfloat16" else 0
+    assert over <= allowed, f"{what}: {over} of {len(got)} rows are beyond {TOLERANCE[dtype]:.0e} of max|logit| (allowed {allowed:.0f})"
+    if dtype == "bfloat16":
+        assert float(np.median(errs)) < BF16_MEDIAN, f"{what}: the median row differs by {np.median(errs):.2e} of max|logit|"
+    return max(errs)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(td.CONFIGS))
+def test_layers_one_by_one(ddirs, name, dtype):
+    """The residual stream after the embedding and after every layer against the plain model's, so that a wrong layer is named."""
+    from inference_bench_b200.engine.step import StepEntry
+    toks = _requests(name)["e"]
+    cfg, w = _weights(name)
+    want = P.hidden_states(toks, cfg, w)
+    runner = _runner(ddirs[name], dtype, 128, td.CONFIGS[name]["page_size"])
+    runner.cache.admit("x")
+    layers = []
+    runner.step([StepEntry("x", toks, list(range(len(toks))))], trace=layers)
+    assert len(layers) == len(want)
+    for i, (g, wv) in enumerate(zip(layers, want)):
+        err = (g.cpu().double() - wv).abs().amax(dim=1) / wv.abs().max().item()
+        where = f"{name}/{dtype}: the stream after layer {i - 1}"
+        if dtype == "float32":
+            assert err.max().item() < 2e-5, f"{where} differs by {err.max().item():.2e}"
+        else:
+            assert err.median().item() < BF16_MEDIAN and (err > 4e-2).sum().item() <= max(3, BF16_ROWS_OVER * len(toks)) and err.max().item() < BF16_WORST, \
+                f"{where} differs by {err.max().item():.2e} (median {err.median().item():.2e})"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(td.CONFIGS))
+@pytest.mark.parametrize("cut", ["whole", "tail", "portions", "mixed"])
+def test_cut_matches_plain(ddirs, plain_logits, name, dtype, cut):
+    """Whole prompts; prompts then the last tokens one by one (a tail long enough for every short window to pass over decoded tokens only);
+    portions down to two tokens; up to four live requests of unequal length in one batch with a pool that only holds what is live, so pages
+    and slots are used again by later requests."""
+    reqs = _requests(name)
+    steps = {"whole": traces.whole, "tail": lambda r: traces.tail_one_by_one(r, tail=60), "portions": traces.portions, "mixed": traces.mixed}[cut](reqs)
+    max_tokens = traces.max_live_tokens(steps)
+    runner = _runner(ddirs[name], dtype, max_tokens, td.CONFIGS[name]["page_size"], max_requests=4)
+    got = traces.run_steps(runner, steps)
+    worst = _compare(got, plain_logits[name], dtype, f"{name}/{dtype}/{cut}")
+    runner.cache.check()
+    assert runner.cache.used_pages() == [0] * len(runner.cache.groups)
+    print(f"{name}/{dtype}/{cut}: worst {worst:.3e} of max|logit|, pool {max_tokens} tokens")
+
+
+def test_a_request_alone_and_in_a_batch_give_the_same_float32_logits(ddirs):
+    """The float32 path adds in one order whatever shares the step: a request beside three others of other lengths, on other pages and
+    in another slot, gives the bits it gives alone."""
+    from inference_bench_b200.engine.step import StepEntry
+    name = "A"
+    reqs = _requests(name)
+    runner = _runner(ddirs[name], "float32", 1024, 16, max_requests=4)
+    runner.cache.admit("alone")
+    alone = runner.step([StepEntry("alone", reqs["d"], [len(reqs["d"]) - 1])]).cpu()
+    runner.cache.release("alone")
+    for r in ("c", "f", "d", "a"):
+        runner.cache.admit(r)
+    rows = runner.step([StepEntry(r, reqs[r], [len(reqs[r]) - 1]) for r in ("c", "f", "d", "a")]).cpu()
+    assert torch.equal(rows[2], alone[0])
+
+
+# ------------------------------------------------------------------------------------------ weights made so that a fault shows
+def _one_layer(tmp_path, kind, mixer, tag, seed=77, mlp=None):
+    cfg = {"architecture": "Ditalorn", "vocab": 64, "width": 64, "max_positions": 400, "embedding": {"scale": 2.0}, "norm": {"eps": 1e-5},
+           "layers": [{"type": kind, "mixer": mixer, "mlp": mlp}]}
+    w = td.tensors(cfg, seed)
+    return cfg, w, lambda: td.write_model("A", tmp_path / tag, config=cfg, weights=w)
+
+
+@pytest.mark.parametrize("window,page", [(16, 16), (7, 16), (33, 8), (1, 16)])
+def test_a_window_that_is_one_position_off_shows(tmp_path, window, page):
+    """One latent-attention layer whose queries and keys are scaled up, so that the softmax puts nearly all of its weight on one key: a window one
+    position too long or too short changes the logits by far more than the tolerance. The engine matches the plain model with the right window and
+    differs from the plain model with either wrong one, in a prompt and while decoding."""
+    mixer = {"heads": 2, "dim": 16, "vdim": 16, "kv_rank": 32, "q_rank": 16, "scale": 1.0, "mask": {"size": window}}
+    cfg, w, write = _one_layer(tmp_path, "latent_attention", mixer, f"w{window}")
+    w["l0.mix.uq"] = (w["l0.mix.uq"].float() * 6).to(torch.bfloat16)
+    w["l0.mix.uk"] = (w["l0.mix.uk"].float() * 6).to(torch.bfloat16)
+    toks = traces.prompt(9, 90, 64)
+    want = P.logits(toks, cfg, w).numpy()
+    steps = traces.tail_one_by_one({"x": toks}, tail=40)
+    runner = _runner(write(), "float32", 128, page)
+    got = traces.run_steps(runner, steps)
+    scale = np.abs(want).max()
+    assert max(np.abs(row - want[pos]).max() for (_, pos), row in got.items()) / scale < 1e-4
+    for wrong in (window + 1, window - 1):
+        if wrong < 1:
+            continue
+        other = copy.deepcopy(cfg)
+        other["layers"][0]["mixer"]["mask"]["size"] = wrong
+        off = P.logits(toks, other, w).numpy()
+        late = [pos for pos in range(len(toks)) if pos >= max(window, wrong)]
+        assert max(np.abs(off[pos] - want[pos]).max() for pos in late) / scale > 1e-2
+
+
+def test_a_far_key_a_lost_state_row_and_a_left_out_bias_show(tmp_path):
+    """One sigmoid-attention layer: the plain model without the convolution's state at a portion's start, without the distance bias, without the bias
+    per head, or with a temperature whose period is one off differs from the right one by far more than the tolerance, and the engine matches the
+    right one under portions of two to seven tokens."""
+    mixer = {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 24, "scale": 0.5, "conv": 3, "q_temp": {"coef": 1.0, "every": 11}}
+    cfg, w, write = _one_layer(tmp_path, "attention", mixer, "sig")
+    toks = traces.prompt(11, 120, 64)
+    want = P.logits(toks, cfg, w).numpy()
+    scale = np.abs(want).max()
+    runner = _runner(write(), "float32", 128, 16)
+    got = traces.run_steps(runner, traces.portions({"x": toks}))
+    assert max(np.abs(row - want[pos]).max() for (_, pos), row in got.items()) / scale < 1e-4
+    for change in ("r1", "pb", "every", "conv"):
+        w2, cfg2 = dict(w), copy.deepcopy(cfg)
+        if change == "r1":
+            w2["l0.mix.r1"] = torch.zeros_like(w["l0.mix.r1"])
+        elif change == "pb":
+            w2["l0.mix.pb"] = torch.zeros_like(w["l0.mix.pb"])
+        elif change == "every":
+            cfg2["layers"][0]["mixer"]["q_temp"]["every"] = 12
+        else:   # a convolution that forgets what came before a portion: the plain model on the last seven tokens alone, at their first position's tap
+            for n in ("q", "k", "v"):
+                t = w[f"l0.mix.{n}.conv"].clone()
+                t[:, :2] = 0
+                w2[f"l0.mix.{n}.conv"] = t
+        off = P.logits(toks, cfg2, w2).numpy()
+        assert np.abs(off[20:] - want[20:]).max() / scale > 1e-2, change
+
+
+# ------------------------------------------------------------------------------------------ generation
+@pytest.mark.parametrize("name", list(td.CONFIGS))
+@pytest.mark.parametrize("graphs", [False, True])
+def test_greedy_generation_through_the_engine(ddirs, name, graphs):
+    """`Engine.generate`: the scheduler cuts prompts into portions, batches them beside decoded tokens, and decode steps run as captured
+    graphs or not; float32 tokens equal the plain model's."""
+    from inference_bench_b200 import Engine
+    cfg, w = _weights(name)
+    prompts = [traces.prompt(70 + i, n, cfg["vocab"]) for i, n in enumerate((5, 21, 40))]
+    want = [P.greedy(p, 7, cfg, w) for p in prompts]
+    eng = Engine(ddirs[name], dtype="float32", max_ctx=128, page_size=td.CONFIGS[name]["page_size"], use_graphs=graphs, prefill_chunk=9, max_batched_tokens=16)
+    got = eng.generate(prompts, max_tokens=7)
+    assert [r.tokens for r in got] == want
+    assert eng.cache.used_pages() == [0] * len(eng.cache.groups)
+    eng.cache.check()
+    one = eng.generate(prompts[1], max_tokens=7)
+    assert one.tokens == want[1]
+
+
+def test_generation_in_bfloat16_runs_and_long_decoding_stays_close(ddirs):
+    from inference_bench_b200 import Engine
+    name = "C"
+    cfg, w = _weights(name)
+    prompt = traces.prompt(5, 12, cfg["vocab"])
+    eng = Engine(ddirs[name], dtype="bfloat16", max_ctx=256, page_size=16)
+    got = eng.generate(prompt, max_tokens=120).tokens
+    assert len(got) == 120
+    lg = P.logits(prompt + got, cfg, w)     # teacher-forced on the engine's own tokens, the plain model ranks every chosen token near the top
+    span = float(lg.max() - lg.min())
+    below = [float(lg[len(prompt) + i - 1].max() - lg[len(prompt) + i - 1][tok]) / span for i, tok in enumerate(got)]
+    assert all(math.isfinite(b) for b in below) and max(below) < 0.2
+    assert sum(b > 0.03 for b in below) <= 0.1 * len(got)
+
+
+def test_trace_replay_program_and_command_line(ddirs, tmp_path):
+    """bin/trace_run as a subprocess fed JSON steps (a mixed trace, float32), and `run` and `spec` of the command line, on a model folder
+    of this architecture: nothing in them names an architecture."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    name = "A"
+    cfg, w = _weights(name)
+    vocab = cfg["vocab"]
+    reqs = {r: traces.prompt(900 + i, n, vocab) for i, (r, n) in enumerate({"a": 70, "b": 9, "c": 33, "d": 64, "e": 2}.items())}
+    steps = traces.mixed(reqs, seed=5)
+    out = tmp_path / "out"
+    proc = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(ddirs[name]), "--dtype", "float32", "--out", str(out),
+                           "--max-tokens", str(traces.max_live_tokens(steps))],
+                          input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    want = {r: P.logits(t, cfg, w).numpy() for r, t in reqs.items()}
+    at = {r: 0 for r in reqs}
+    for s in steps:
+        rows = np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(-1, vocab)
+        k = 0
+        for e in s["entries"]:
+            for wi in e["want"]:
+                err = np.abs(rows[k] - want[e["id"]][at[e["id"]] + wi]).max() / np.abs(want[e["id"]]).max()
+                assert err <= TOLERANCE["float32"]
+                k += 1
+            at[e["id"]] += len(e["tokens"])
+        assert k == rows.shape[0]
+    env = dict(os.environ, PYTHONPATH=root)
+    p = subprocess.run([sys.executable, "-m", "inference_bench_b200", "run", "--model", str(ddirs[name]), "--prompt-len", "12", "--max-tokens", "5", "--json",
+                        "--dtype", "float32", "--max-ctx", "64"], capture_output=True, text=True, env=env, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    r = json.loads(p.stdout)
+    from inference_bench_b200.cli import _synthetic_prompt
+    assert r["prompt_tokens"] == 12 and r["tokens"] == P.greedy(_synthetic_prompt(12, vocab), 5, cfg, w)
+    p = subprocess.run([sys.executable, "-m", "inference_bench_b200", "spec", "--model", str(ddirs[name])], capture_output=True, text=True, env=env)
+    assert p.returncode == 0 and json.loads(p.stdout)["layers"][1]["mixer"]["mask"]["size"] == 9
