@@ -434,6 +434,55 @@ DESIGN_KINDS = {   # kinds of kernel by the library entry points that launch the
                 "norm": ["ib_add_rmsnorm", "ib_add_rmsnorm_ext", "ib_token_shift_rows", "ib_qk_norm_rope_kv", "ib_loop_pack", "ib_xielu_rows", "ib_add_bias_rows"],
                 "gemm": LEAVE_OUT["gemm"] + ["ib_gemm_xielu_tcgen05"]},
 }
+# Ditalorn at the sizes above (the same width, heads, latent and experts as the Zabonex shape it stands beside): layers alternate between windowed
+# latent attention with a query latent and grouped attention with sigmoid weights behind a convolution of four taps; every feed-forward is routed.
+DITALORN_SIZES = {
+    "small": dict(DESIGN_SIZES["small"], q_rank=384, window=1024, att_heads=8, att_kv_heads=2, att_dim=128, att_vdim=128, conv=4),
+    "lite": dict(DESIGN_SIZES["lite"], q_rank=768, window=1024, att_heads=16, att_kv_heads=4, att_dim=128, att_vdim=128, conv=4),
+}
+DESIGN_KINDS["ditalorn"] = {
+    "attention": ["ib_latent_attention", "ib_latent_attention_mma"], "sigmoid": ["ib_sigmoid_attention", "ib_sigmoid_attention_mma"],
+    "experts": ["ib_gemm_grouped", "ib_gemm_grouped_mma", "ib_gemm_grouped_tcgen05", "ib_gemm_grouped_swiglu_tcgen05", "ib_gather_rows"],
+    "heads": ["ib_gemm_heads", "ib_gemm_heads_mma"], "route": ["ib_moe_route", "ib_moe_sort", "ib_moe_combine"],
+    "norm": ["ib_add_rmsnorm", "ib_post_norm", "ib_latent_down", "ib_latent_prepare", "ib_qkv_conv", "ib_embed_pos"], "gemm": LEAVE_OUT["gemm"]}
+
+
+def ditalorn_config(z: dict, layers: int) -> dict:
+    lat = {"heads": z["heads"], "dim": z["dim"], "vdim": z["vdim"], "kv_rank": z["rank"], "q_rank": z["q_rank"], "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]}}
+    att = {"heads": z["att_heads"], "kv_heads": z["att_kv_heads"], "dim": z["att_dim"], "vdim": z["att_vdim"], "scale": z["att_dim"] ** -0.5, "conv": z["conv"],
+           "q_temp": {"coef": 0.5, "every": 128}}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["groups"][0], "keep": z["groups"][1]}}}
+    ls = [{"type": "attention" if i % 2 else "latent_attention", "mixer": att if i % 2 else lat, "mlp": moe} for i in range(layers)]
+    return {"architecture": "Ditalorn", "vocab": z["vocab"], "width": z["width"], "max_positions": CONTEXT, "embedding": {"scale": z["width"] ** 0.5}, "norm": {"eps": 1e-6},
+            "layers": ls}
+
+
+def ditalorn_work(z: dict, layers: int, T: int, ctx: int, batch: int) -> tuple:
+    """Algorithmic FLOPs and bytes of the design's kinds of kernel for a prefill of T tokens and for a decode step of `batch` requests at `ctx`
+    tokens of context (per step, all layers), and the single-matrix products' weights (elements)."""
+    n_att = layers // 2
+    n_lat = layers - n_att
+    W, H, r, win = z["width"], z["heads"], z["rank"], z["window"]
+    AH, AG, AD, AV = z["att_heads"], z["att_kv_heads"], z["att_dim"], z["att_vdim"]
+    pairs_w = sum(min(t + 1, win) for t in range(T))
+    pairs = T * (T + 1) / 2
+    seen = min(ctx, win)
+    R = (AH + AG) * AD + AG * AV
+    norm_row = layers * W * (4.0 * 4 + 2 + 4 + 4 + 2) + n_lat * (4.0 * (z["q_rank"] + r) + 2 * (z["q_rank"] + r) + 6.0 * H * z["dim"]) + n_att * R * (4.0 * z["conv"] + 2)
+    lin = n_lat * ((z["q_rank"] + r + H) * W + H * z["dim"] * z["q_rank"] + H * z["vdim"] * W) + n_att * (R * W + AH * AV * W) + layers * z["experts"] * W + z["vocab"] * W
+    work = {
+        "prefill": {"attention": {"flops": n_lat * 4.0 * H * pairs_w * r}, "sigmoid": {"flops": n_att * 2.0 * AH * pairs * (AD + AV)},
+                    "experts": {"flops": layers * 2.0 * T * z["top"] * 3 * z["expert_ff"] * W},
+                    "heads": {"flops": n_lat * 2.0 * T * H * r * (z["dim"] + z["vdim"])}, "norm": {"flops": 0.0, "bytes": T * norm_row}},
+        "decode": {"attention": {"flops": n_lat * 4.0 * H * batch * seen * r, "bytes": n_lat * 2.0 * batch * seen * r},
+                   "sigmoid": {"flops": n_att * 2.0 * AH * batch * ctx * (AD + AV), "bytes": n_att * 2.0 * batch * ctx * AG * (AD + AV)},
+                   "experts": {"flops": layers * 2.0 * batch * z["top"] * 3 * z["expert_ff"] * W, "bytes": layers * 2.0 * min(batch * z["top"], z["experts"]) * 3 * z["expert_ff"] * W},
+                   "heads": {"flops": n_lat * 2.0 * batch * H * r * (z["dim"] + z["vdim"]), "bytes": n_lat * 2.0 * H * r * (z["dim"] + z["vdim"])},
+                   "norm": {"flops": 0.0, "bytes": batch * norm_row}},
+    }
+    return work, lin
+
+
 # Busadra at layer sizes that resemble small hybrid models: windowed grouped-query attention with heads of 128, a gated linear recurrence
 # whose heads hold a 128 x 128 state, and routed experts; layers in the order attention, recurrence, recurrence, attention (repeated).
 BUSADRA_SIZES = {
@@ -646,7 +695,7 @@ def run_design(args) -> dict:
     layers = args.layers or 4
     steps, warmup = min(args.steps, 32), max(args.warmup, 3)
     out = {"design": args.design, "layers": layers, "peaks": pk_src, "sizes": {}}
-    sizes = {"busadra": BUSADRA_SIZES, "lulenex": LULENEX_SIZES}.get(args.design, DESIGN_SIZES)
+    sizes = {"busadra": BUSADRA_SIZES, "lulenex": LULENEX_SIZES, "ditalorn": DITALORN_SIZES}.get(args.design, DESIGN_SIZES)
     for name in (args.size.split(",") if args.size else list(sizes)):
         z = sizes[name] if name in sizes or args.design != "lulenex" else LULENEX_EXTRA_SIZES[name]
         report = {}
@@ -656,6 +705,8 @@ def run_design(args) -> dict:
         elif args.design == "busadra":
             zb = z
             pair = (("busadra", busadra_config(z, layers)), ("qwen3", qwen3_like_busadra(z, layers)))
+        elif args.design == "ditalorn":
+            pair = (("ditalorn", ditalorn_config(z, layers)), ("zabonex", zabonex_config(z, layers)))
         else:
             pair = (("zabonex", zabonex_config(z, layers)), ("qwen3", qwen3_like(z, layers)))
         for arch, cfg in pair:
@@ -668,6 +719,8 @@ def run_design(args) -> dict:
                     3 * z["dense_ff"] * z["width"] + (layers - 1) * (3 * z["shared_ff"] + z["experts"]) * z["width"] + vocab * z["width"]
             elif arch == "lulenex":
                 work, lin = lulenex_work(z, layers, PROMPT, PROMPT, 8)
+            elif arch == "ditalorn":
+                work, lin = ditalorn_work(z, layers, PROMPT, PROMPT, 8)
             elif arch == "busadra":
                 work = busadra_work(zb, layers, PROMPT, PROMPT, 8)
                 n_att = sum(1 for i in range(layers) if i % 4 in (0, 3))
@@ -738,9 +791,9 @@ def main() -> int:
     ap.add_argument("--leave-out", default="", help="with --only decode or prefill: also time the step without each of these kinds of kernel (comma separated; "
                     "a+b leaves both out): " + ", ".join(sorted(LEAVE_OUT)))
     ap.add_argument("--only", default="", choices=["", "prefill", "decode", "mixed"], help="run one part alone (for profiling); prints a short report")
-    ap.add_argument("--design", default="", choices=["", "zabonex", "busadra", "lulenex"],
-                    help="measure another design beside the closest existing one at equal size (Qwen3; for lulenex, Busadra) instead of the benchmark (prints its own report)")
-    ap.add_argument("--size", default="", help="with --design: which of its sizes (comma separated; default all): " + ", ".join(DESIGN_SIZES) + " (zabonex); " + ", ".join(BUSADRA_SIZES) + " (busadra); " + ", ".join(LULENEX_SIZES) + " (lulenex)")
+    ap.add_argument("--design", default="", choices=["", "zabonex", "busadra", "lulenex", "ditalorn"],
+                    help="measure another design beside the closest existing one at equal size (Qwen3; for lulenex, Busadra; for ditalorn, Zabonex) instead of the benchmark (prints its own report)")
+    ap.add_argument("--size", default="", help="with --design: which of its sizes (comma separated; default all): " + ", ".join(DESIGN_SIZES) + " (zabonex); " + ", ".join(BUSADRA_SIZES) + " (busadra); " + ", ".join(LULENEX_SIZES) + " (lulenex); " + ", ".join(DITALORN_SIZES) + " (ditalorn)")
     args = ap.parse_args()
     if args.design:
         print(json.dumps(run_design(args)))

@@ -959,21 +959,22 @@ def selective_scan(xc: torch.Tensor, low: torch.Tensor, proj: torch.Tensor, wdt:
 
 # ---------------------------------------------------------------- attention with sigmoid weights behind a convolution of its projections (csrc/sigmoid_attention.cu)
 L.register("ib_qkv_conv", [L._p, L._i, L._ll, L._p, L._p, L._i, L._p, L._ll, L._p, L._p, L._p, L._i, L._p, L._i, L._i, L._i, L._i, L._f, L._i, L._i, L._f, L._p, L._i,
-                           C.POINTER(L.KvView), L._p, L._p])
+                           C.POINTER(L.KvView), L._p, L._i, L._p])
 L.register("ib_sigmoid_attention", [L._p, L._i, C.POINTER(L.KvView), L._p, L._p, L._f, L._p, L._p, L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._i, L._p, L._p])
-L.register("ib_sigmoid_attention_mma", [L._p, C.POINTER(L.KvView), L._p, L._p, L._p, L._i, L._f, L._p, L._p, L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._i, L._p, L._p])
+L.register("ib_sigmoid_attention_mma", [L._p, C.POINTER(L.KvView), L._p, L._p, L._p, L._i, L._i, L._f, L._p, L._p, L._p, L._p, L._p, L._i, L._i, L._i, L._i, L._i, L._i, L._p, L._p])
 L.KERNELS_PER_CALL["ib_qkv_conv"] = 1   # two with a convolution state; counted by the caller
 
 
 def qkv_conv(proj: torch.Tensor, bias: Optional[torch.Tensor], conv_w: Optional[torch.Tensor], conv_state: Optional[torch.Tensor], seg_of_token: torch.Tensor,
              seg_start: torch.Tensor, seg_slot: torch.Tensor, n_segments: int, positions: torch.Tensor, q_out: torch.Tensor, kv: KvLayerView, heads: int, qk_dim: int,
-             v_dim: int, status: torch.Tensor, q_temp: Optional[tuple] = None, v_norm: bool = False, eps: float = 0.0) -> None:
+             v_dim: int, status: torch.Tensor, q_temp: Optional[tuple] = None, v_norm: bool = False, eps: float = 0.0, single_tokens: bool = False) -> None:
     """proj float32 [P, T, R] with R = [heads x qk_dim | kv_heads x qk_dim | kv_heads x v_dim], bias float32 [R] or None.
     conv_w float32 [taps, R] (a tap's weights for all channels together; the last row is the current token's) or None for no convolution;
     conv_state float32 [slots, taps - 1, R]: the last rows of the biased projection of every request, read for the rows before a segment's
     first token and then replaced by the step's last rows. q_temp = (coef, every): q is multiplied by 1 + coef ln(floor((p + 1) / every) + 1)
     at position p. v_norm: every value head is divided by its root mean square (eps inside the root). Writes q_out [T, heads * qk_dim] in
-    the activation dtype and the keys and values into the paged cache."""
+    the activation dtype and the keys and values into the paged cache. single_tokens: every segment brings one token (a step of decoded
+    tokens): the state is replaced inside the one kernel; otherwise a second kernel does it after every reader of the old state."""
     _check("proj", proj, torch.float32)
     P, T, R = proj.shape
     view = kv.c_view()
@@ -994,28 +995,34 @@ def qkv_conv(proj: torch.Tensor, bias: Optional[torch.Tensor], conv_w: Optional[
         if tuple(conv_state.shape[1:]) != (taps - 1, R):
             raise L.KernelError(f"qkv_conv: conv_state must be [slots, {taps - 1}, {R}], got {tuple(conv_state.shape)}")
         slot_stride = conv_state.stride(0)
-        L.launches += 1
+        if not single_tokens:
+            L.launches += 1
     for name, t_, n in (("seg_of_token", seg_of_token, T), ("positions", positions, T), ("seg_start", seg_start, n_segments + 1), ("seg_slot", seg_slot, n_segments)):
         _check(name, t_, torch.int32, (n,))
     coef, every = (0.0, 0) if q_temp is None else (float(q_temp[0]), int(q_temp[1]))
     L.call("ib_qkv_conv", proj.data_ptr(), P, T * R, _ptr(bias), _ptr(conv_w), taps, _ptr(conv_state) if taps > 1 else None, slot_stride, seg_of_token.data_ptr(),
            seg_start.data_ptr(), seg_slot.data_ptr(), n_segments, positions.data_ptr(), T, heads, qk_dim, v_dim, coef, every, 1 if v_norm else 0, float(eps),
-           q_out.data_ptr(), dtype_code(q_out.dtype), C.byref(view), status.data_ptr(), _stream())
+           q_out.data_ptr(), dtype_code(q_out.dtype), C.byref(view), status.data_ptr(), 1 if single_tokens else 0, _stream())
 
 
 def sigmoid_attention_mma_supports(heads: int, kv_heads: int, qk_dim: int, v_dim: int) -> bool:
     return bool(L.load().ib_sigmoid_attention_mma_supports(int(heads), int(kv_heads), int(qk_dim), int(v_dim)))
 
 
+def sigmoid_attention_mma_rows(qk_dim: int, v_dim: int, rows_wanted: int) -> int:
+    """Query rows a CTA of the tensor-core kernel holds (16, 32 or 64) when `rows_wanted` rows of a step can share key and value tiles."""
+    return int(L.load().ib_sigmoid_attention_mma_rows(int(qk_dim), int(v_dim), int(rows_wanted)))
+
+
 def sigmoid_attention(q: torch.Tensor, kv: KvLayerView, positions: torch.Tensor, seg_of_token: torch.Tensor, scale: float, r1: Optional[torch.Tensor],
                       r2: Optional[torch.Tensor], pb: Optional[torch.Tensor], out: torch.Tensor, heads: int, qk_dim: int, v_dim: int, status: torch.Tensor,
                       n_slices: int = 1, slice_keys: int = 1 << 30, part: Optional[torch.Tensor] = None, units: Optional[torch.Tensor] = None,
-                      tensor_cores: bool = False) -> None:
+                      tensor_cores: bool = False, rows: int = 16) -> None:
     """out[t, h] = sum over keys j <= position of sigmoid((q . k_j) * scale - r1[h] ln(1 + r2[h] (position - j)) + pb[h]) v_j: causal attention whose
     weights are sigmoids and are not normalised. r1, r2, pb: float32 [heads] or None. n_slices > 1: the keys are cut into slices of slice_keys whose
     partial sums (`part`, float32, at least T * heads * n_slices * v_dim values) are added in order. tensor_cores: the m16n8k16 kernel (bfloat16; see
     `sigmoid_attention_mma_supports`), with `units` None (a CTA per token and kv head) or int32 [n, 2] of (first token, tokens) runs of consecutive
-    tokens of one request, at most 16 // (heads // kv_heads) tokens each."""
+    tokens of one request, at most rows // (heads // kv_heads) tokens each; rows: query rows a CTA holds (`sigmoid_attention_mma_rows`)."""
     T = q.shape[0]
     view = kv.c_view()
     _check("q", q, None, (T, heads * qk_dim))
@@ -1035,7 +1042,7 @@ def sigmoid_attention(q: torch.Tensor, kv: KvLayerView, positions: torch.Tensor,
         if units is not None:
             _check("units", units, torch.int32)
             n_units = units.shape[0]
-        L.call("ib_sigmoid_attention_mma", q.data_ptr(), C.byref(view), positions.data_ptr(), seg_of_token.data_ptr(), _ptr(units), n_units, float(scale), _ptr(r1), _ptr(r2),
+        L.call("ib_sigmoid_attention_mma", q.data_ptr(), C.byref(view), positions.data_ptr(), seg_of_token.data_ptr(), _ptr(units), n_units, int(rows), float(scale), _ptr(r1), _ptr(r2),
                _ptr(pb), out.data_ptr(), _ptr(part), T, heads, qk_dim, v_dim, n_slices, slice_keys, status.data_ptr(), _stream())
         return
     L.call("ib_sigmoid_attention", q.data_ptr(), dtype_code(q.dtype), C.byref(view), positions.data_ptr(), seg_of_token.data_ptr(), float(scale), _ptr(r1), _ptr(r2),

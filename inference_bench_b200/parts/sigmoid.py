@@ -99,7 +99,16 @@ class SigmoidAttention(base.Mixer):
         key = ("sigmoid slices", self.heads, self.kv_heads, tc)
         if key not in ctx.memo:
             out = (1, 1 << 30)
-            if ctx.fixed_shape or ctx.max_segment_len == 1:
+            if tc and not ctx.fixed_shape and ctx.max_segment_len > 1:
+                # prompt portions on the tensor cores: a CTA holds 64 rows and walks their keys in order, so a long context makes a few long chains;
+                # up to eight slices of at least 512 keys side by side shorten them while the step has fewer CTAs than four an SM
+                longest = int(np.max(ctx.h_positions)) + 1
+                ctas = -(-ctx.n_tokens * self.heads // 64)
+                if longest > 1024 and ctas < 4 * ctx.rt.sm_count and max(self.dim, self.vdim) <= 128:
+                    n = min(8, -(-longest // 512))
+                    per = -(-(-(-longest // n)) // 64) * 64
+                    out = (-(-longest // per), per)
+            elif ctx.fixed_shape or ctx.max_segment_len == 1:
                 max_keys = view.table_stride * view.page_size if ctx.fixed_shape else int(np.max(ctx.h_positions)) + 1
                 ctas = ctx.n_tokens * self.kv_heads if tc else -(-ctx.n_tokens * self.heads // 4)
                 n = max(1, min(2 * ctx.rt.sm_count // max(ctas, 1), -(-max_keys // 128)))
@@ -128,7 +137,8 @@ class SigmoidAttention(base.Mixer):
         proj = rt.linear(h, self.wqkv)                                       # [P, T, row] = u without its bias
         q = rt.empty((T, self.heads * self.dim))
         ops.qkv_conv(proj, self.qkv_bias, self.conv_w, state, ctx.seg_of_token, ctx.seg_start, ctx.seg_slot, ctx.n_segments, ctx.positions, q, pages, self.heads,
-                     self.dim, self.vdim, rt.status, q_temp=self.q_temp, v_norm=self.value_norm, eps=self.norm_eps)
+                     self.dim, self.vdim, rt.status, q_temp=self.q_temp, v_norm=self.value_norm, eps=self.norm_eps,
+                     single_tokens=ctx.fixed_shape or ctx.n_segments == T)
         tc = self._tensor_cores(rt)
         n_slices, slice_keys = self._slices(ctx, pages.c_view(), tc)
         part = None
@@ -138,7 +148,11 @@ class SigmoidAttention(base.Mixer):
                 ctx.memo[skey] = rt.empty((T * self.heads * n_slices * self.vdim,), torch.float32)
             part = ctx.memo[skey]
         out = rt.empty((T, self.heads * self.vdim))
-        units = self._units(ctx, 16 // (self.heads // self.kv_heads)) if tc else None
+        rows, units = 16, None
+        if tc:   # a prompt portion: up to 64 rows a CTA (the group's heads of consecutive tokens) share every key and value tile
+            group = self.heads // self.kv_heads
+            rows = ops.sigmoid_attention_mma_rows(self.dim, self.vdim, group * (1 if ctx.fixed_shape else ctx.max_segment_len))
+            units = self._units(ctx, rows // group)
         ops.sigmoid_attention(q, pages, ctx.positions, ctx.seg_of_token, self.scale, self.r1, self.r2, self.pb, out, self.heads, self.dim, self.vdim, rt.status,
-                              n_slices=n_slices, slice_keys=slice_keys, part=part, units=units, tensor_cores=tc)
+                              n_slices=n_slices, slice_keys=slice_keys, part=part, units=units, tensor_cores=tc, rows=rows)
         return rt.linear(out, self.wo)

@@ -243,6 +243,7 @@ def test_sigmoid_attention_far_keys_and_the_causal_edge(rt32, rt16, dtype, heads
     pool, perm = _paged([pad(k), pad(v)], page, dtype, g)
     tc = dtype == torch.bfloat16 and ops.sigmoid_attention_mma_supports(heads, kv_heads, dim, vdim)
     for runs, slices in (([(100, 130), (0, 7), (320, 1), (321, 1), (2 * page - 2, 4), (280, 40)], (1, 1 << 30)), ([(320, 1), (300, 1), (0, 1), (150, 1)], (4, 128)),
+                         ([(100, 130), (0, 7), (320, 1), (2 * page - 2, 4), (280, 40)], (3, 128)),
                          ([(200, 1), (2 * page, 1)], (1, 1 << 30))):
         positions = [p0 + i for p0, n in runs for i in range(n)]
         T = len(positions)
@@ -254,7 +255,8 @@ def test_sigmoid_attention_far_keys_and_the_causal_edge(rt32, rt16, dtype, heads
         n_slices, slice_keys = slices
         part = torch.empty((T * heads * n_slices * vdim,), dtype=torch.float32, device=DEV)
         units = None
-        per = 16 // group if tc else 1
+        rows = ops.sigmoid_attention_mma_rows(dim, vdim, group * max(n for _, n in runs)) if tc else 16
+        per = rows // group if tc else 1
         if per > 1 and max(n for _, n in runs) > 1:
             u, t0 = [], 0
             for _, n in runs:
@@ -262,7 +264,7 @@ def test_sigmoid_attention_far_keys_and_the_causal_edge(rt32, rt16, dtype, heads
                 t0 += n
             units = torch.tensor(u, dtype=torch.int32, device=DEV)
         ops.sigmoid_attention(qd, view, ctx.positions, ctx.seg_of_token, scale, _f32(r1), _f32(r2), _f32(pb), out, heads, dim, vdim, rt.status, n_slices=n_slices,
-                              slice_keys=slice_keys, part=part, units=units, tensor_cores=tc)
+                              slice_keys=slice_keys, part=part, units=units, tensor_cores=tc, rows=rows)
         got = out.float().cpu().double().view(T, heads, vdim)
         ref = want[positions]
         tol = 5e-5 if dtype == torch.float32 else 2e-2
@@ -319,7 +321,7 @@ def test_convolution_of_projections_over_portions_and_slots(rt32, rt16, dtype, h
         view = KvLayerView(pool, 0, table.to(DEV))
         q_out = torch.empty((T, heads * dim), dtype=dtype, device=DEV)
         ops.qkv_conv(proj, _f32(bias), _f32(conv.t()), state, ctx.seg_of_token, ctx.seg_start, ctx.seg_slot, len(step), ctx.positions, q_out, view, heads, dim, vdim, rt.status,
-                     q_temp=(coef, every) if every else None, v_norm=True, eps=eps)
+                     q_temp=(coef, every) if every else None, v_norm=True, eps=eps, single_tokens=all(n == 1 for _, n in step))
         t0 = 0
         for r, n in step:
             got_q = q_out[t0:t0 + n].float().cpu().double().view(n, heads, dim)
