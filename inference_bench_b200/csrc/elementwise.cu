@@ -313,37 +313,64 @@ __global__ void norm_residual_kernel(float* __restrict__ x, const float* __restr
 //   y = sum_p delta[p][t] + bias;   v = x[t] + w_post * (y * rsqrt(mean(y^2) + eps))        (without delta: v = x[t])
 //   x[t] = v  (unless rows gathers);   out[r] = w_next * (v * rsqrt(mean(v^2) + eps))       (without out: the add alone)
 // The row lives in shared memory between the passes; all arithmetic float32, sums in an order that depends on H alone.
-template <typename O>
+template <typename O, int VEC>
 __global__ void post_norm_kernel(float* __restrict__ x, const float* __restrict__ delta, int P, size_t delta_stride, const float* __restrict__ bias,
                                  const float* __restrict__ w_post, const float* __restrict__ w_next, float eps, O* __restrict__ out,
                                  const int* __restrict__ rows, int H) {
+  // VEC = 4 when H is a multiple of 4 and every pointer is 16-byte aligned (16-byte accesses), else 1. A thread adds the squares of its
+  // values in rising order either way; the order of a row's sums depends on H and VEC alone.
   extern __shared__ __align__(16) float row[];
   __shared__ float scratch[32];
   ib::pdl_launch_dependents();
   ib::pdl_wait();
   const int r = blockIdx.x, t = rows ? rows[r] : r;
   float* xr = x + (size_t)t * H;
+  const int n = H / VEC;
+  using V = std::conditional_t<VEC == 4, float4, float>;
+  auto get = [](const V& v, int k) -> float {
+    if constexpr (VEC == 4) return k == 0 ? v.x : (k == 1 ? v.y : (k == 2 ? v.z : v.w));
+    else return v;
+  };
+  auto put = [](V& v, int k, float a) {
+    if constexpr (VEC == 4) (k == 0 ? v.x : (k == 1 ? v.y : (k == 2 ? v.z : v.w))) = a;
+    else v = a;
+  };
   float inv = 0.f;
   if (delta) {
-    const float* dr = delta + (size_t)t * H;
+    const V* dr = (const V*)(delta + (size_t)t * H);
     float ss = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-      float d = dr[i];
-      for (int p = 1; p < P; p++) d += dr[p * delta_stride + i];
-      if (bias) d += bias[i];
-      row[i] = d;
-      ss = __fmaf_rn(d, d, ss);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      V d = dr[i];
+#pragma unroll 4
+      for (int p = 1; p < P; p++) {
+        const V e = ((const V*)(delta + (size_t)t * H + p * delta_stride))[i];
+#pragma unroll
+        for (int k = 0; k < VEC; k++) put(d, k, get(d, k) + get(e, k));
+      }
+      if (bias) {
+        const V b = ((const V*)bias)[i];
+#pragma unroll
+        for (int k = 0; k < VEC; k++) put(d, k, get(d, k) + get(b, k));
+      }
+      ((V*)row)[i] = d;
+#pragma unroll
+      for (int k = 0; k < VEC; k++) ss = __fmaf_rn(get(d, k), get(d, k), ss);
     }
     ss = ib::block_sum(ss, scratch);
     inv = 1.f / sqrtf(ss / (float)H + eps);
   }
   float s2 = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    float v = xr[i];
-    if (delta) v += w_post[i] * (row[i] * inv);
-    if (!rows) xr[i] = v;
-    row[i] = v;
-    s2 = __fmaf_rn(v, v, s2);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    V v = ((const V*)xr)[i];
+    if (delta) {
+      const V d = ((const V*)row)[i], w = ((const V*)w_post)[i];
+#pragma unroll
+      for (int k = 0; k < VEC; k++) put(v, k, get(v, k) + get(w, k) * (get(d, k) * inv));
+    }
+    if (!rows) ((V*)xr)[i] = v;
+    ((V*)row)[i] = v;
+#pragma unroll
+    for (int k = 0; k < VEC; k++) s2 = __fmaf_rn(get(v, k), get(v, k), s2);
   }
   if (!out) return;
   s2 = ib::block_sum(s2, scratch);
@@ -473,14 +500,22 @@ extern "C" int ib_post_norm(float* x, const float* delta, int P, long long delta
   IB_CHECK_ARG(n_rows > 0 && H > 0 && (!delta || (P >= 1 && w_post)) && (!out || w_next) && (delta || out), "post_norm: bad arguments rows=%d H=%d P=%d", n_rows, H, P);
   const size_t smem = (size_t)H * sizeof(float);
   IB_CHECK_ARG(smem <= 200 * 1024, "post_norm: hidden size %d needs %zu bytes of shared memory, more than 200 KiB", H, smem);
-  const int threads = H >= 2048 ? 1024 : (H >= 1024 ? 512 : 256);
+  const bool vec = H % 4 == 0 && delta_stride % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)delta % 16 == 0 && (uintptr_t)bias % 16 == 0 && (uintptr_t)w_post % 16 == 0;
+  // (a function of H alone: the order of a row's sums must not depend on how many rows share the launch)
+  const int threads = vec ? (H / 4 >= 1024 ? 1024 : (H / 4 <= 128 ? 128 : (H / 4 + 31) / 32 * 32)) : (H >= 2048 ? 1024 : (H >= 1024 ? 512 : 256));
   auto go = [&](auto kernel, auto* o) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     ib::launch(kernel, n_rows, threads, smem, stream, x, delta, P, (size_t)delta_stride, bias, w_post, w_next, eps, o, rows, H);
   };
-  if (!out || out_dtype == IB_F32) go(post_norm_kernel<float>, (float*)out);
-  else if (out_dtype == IB_BF16) go(post_norm_kernel<__nv_bfloat16>, (__nv_bfloat16*)out);
-  else return ib_set_error("post_norm: unknown output dtype %d", out_dtype);
+  if (!out || out_dtype == IB_F32) {
+    if (vec) go(post_norm_kernel<float, 4>, (float*)out);
+    else go(post_norm_kernel<float, 1>, (float*)out);
+  } else if (out_dtype == IB_BF16) {
+    if (vec) go(post_norm_kernel<__nv_bfloat16, 4>, (__nv_bfloat16*)out);
+    else go(post_norm_kernel<__nv_bfloat16, 1>, (__nv_bfloat16*)out);
+  } else {
+    return ib_set_error("post_norm: unknown output dtype %d", out_dtype);
+  }
   IB_CHECK_LAUNCH("post_norm");
   return 0;
 }

@@ -94,58 +94,51 @@ __global__ void latent_prepare_kernel(const float* __restrict__ qd, int P, size_
 }
 
 // The first product of a layer whose queries go through a latent of their own: [c_q raw (q_rank) | c raw (rank) | key part (rot) | ...].
-// Warp 0 of a token norms c_q (weight w_q) into the activation dtype, the operand of the product that makes the heads' queries; warp 1
-// norms the latent, rotates the shared key part and writes the token's cache row. Further columns (gates) are left to their readers.
+// Per token, c_q is normed (weight w_q) into the activation dtype, the operand of the product that makes the heads' queries; the latent is
+// normed, the shared key part rotated, and both written as the token's cache row. Further columns (gates) are left to their readers.
 template <typename A, typename C>
 __global__ void latent_down_kernel(const float* __restrict__ qd, int P, size_t stride_p, int row_len, int q_rank, const float* __restrict__ q_norm_w,
                                    A* __restrict__ cq, const float* __restrict__ c_norm_w, float eps, const float* __restrict__ cos_t,
                                    const float* __restrict__ sin_t, int rot_half, const int* __restrict__ positions, const int* __restrict__ seg_of_token,
                                    IbKvView kv, int rank, int rot, unsigned* __restrict__ status) {
+  // A CTA per token: the partial sums of the row's first q_rank + rank + rot columns are added once (several loads in flight) into shared
+  // memory, the two sums of squares are block sums, and the threads then write the normed query latent and the cache row.
+  extern __shared__ __align__(16) float row[];
+  __shared__ float scratch[32];
   ib::pdl_launch_dependents();
   ib::pdl_wait();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x;
-  const float* row = qd + (size_t)t * row_len;
-  auto summed = [&](int col) {
-    float a = row[col];
-    for (int p = 1; p < P; p++) a += row[p * stride_p + col];
-    return a;
-  };
-  if (warp == 0) {
-    float ss = 0.f;
-    for (int d = lane; d < q_rank; d += 32) {
-      const float a = summed(d);
-      ss = __fmaf_rn(a, a, ss);
-    }
-    ss = ib::warp_sum(ss);
-    const float inv = 1.f / sqrtf(ss / (float)q_rank + eps);
-    for (int d = lane; d < q_rank; d += 32) cq[(size_t)t * q_rank + d] = ib::from_f32<A>(summed(d) * inv * q_norm_w[d]);
-    return;
+  const int t = blockIdx.x, n = q_rank + rank + rot;
+  const float* src = qd + (size_t)t * row_len;
+  float sq = 0.f, sc = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float a = src[i];
+#pragma unroll 4
+    for (int p = 1; p < P; p++) a += src[p * stride_p + i];
+    row[i] = a;
+    if (i < q_rank) sq = __fmaf_rn(a, a, sq);
+    else if (i < q_rank + rank) sc = __fmaf_rn(a, a, sc);
   }
+  sq = ib::block_sum(sq, scratch);
+  sc = ib::block_sum(sc, scratch);
+  const float inv_q = 1.f / sqrtf(sq / (float)q_rank + eps), inv_c = 1.f / sqrtf(sc / (float)rank + eps);
+  for (int d = threadIdx.x; d < q_rank; d += blockDim.x) cq[(size_t)t * q_rank + d] = ib::from_f32<A>(row[d] * inv_q * q_norm_w[d]);
   const long long off = ib::kv_offset(kv, seg_of_token[t], positions[t], 0);
   if (off < 0) {
-    if (lane == 0) atomicOr(status, IB_ERR_BAD_PAGE);
+    if (threadIdx.x == 0) atomicOr(status, IB_ERR_BAD_PAGE);
     return;
   }
   C* dst = (C*)kv.base + off;
-  const int col0 = q_rank;
-  float ss = 0.f;
-  for (int d = lane; d < rank; d += 32) {
-    const float a = summed(col0 + d);
-    ss = __fmaf_rn(a, a, ss);
-  }
-  ss = ib::warp_sum(ss);
-  const float inv = 1.f / sqrtf(ss / (float)rank + eps);
-  for (int d = lane; d < rank; d += 32) dst[d] = ib::from_f32<C>(summed(col0 + d) * inv * c_norm_w[d]);
+  const float* c = row + q_rank;
+  for (int d = threadIdx.x; d < rank; d += blockDim.x) dst[d] = ib::from_f32<C>(c[d] * inv_c * c_norm_w[d]);
   const float* cs = cos_t + (size_t)t * rot_half;
   const float* sn = sin_t + (size_t)t * rot_half;
-  for (int i = lane; 2 * i < rot; i += 32) {
-    const float a = summed(col0 + rank + 2 * i), b = 2 * i + 1 < rot ? summed(col0 + rank + 2 * i + 1) : 0.f;
+  for (int i = threadIdx.x; 2 * i < rot; i += blockDim.x) {
+    const float a = c[rank + 2 * i], b = 2 * i + 1 < rot ? c[rank + 2 * i + 1] : 0.f;
     float x = a, y = b;
     if (i < rot_half) {
-      const float c = cs[i], s = sn[i];
-      x = a * c - b * s;
-      y = b * c + a * s;
+      const float co = cs[i], si = sn[i];
+      x = a * co - b * si;
+      y = b * co + a * si;
     }
     dst[rank + 2 * i] = ib::from_f32<C>(x);
     if (2 * i + 1 < rot) dst[rank + 2 * i + 1] = ib::from_f32<C>(y);
@@ -386,9 +379,12 @@ extern "C" int ib_latent_down(const float* qd, int P, long long stride_p, int ro
   IB_CHECK_ARG(kv->head_dim == rank + rot, "latent_down: the cache row has %d values, expected rank + rot = %d", kv->head_dim, rank + rot);
   IB_CHECK_ARG(2 * rot_half <= rot && row_len >= q_rank + rank + rot, "latent_down: a row of %d columns does not hold %d + %d + %d (turned: %d)", row_len, q_rank, rank,
                rot, 2 * rot_half);
+  const size_t smem = (size_t)(q_rank + rank + rot) * sizeof(float);
+  IB_CHECK_ARG(smem <= 200 * 1024, "latent_down: %d + %d + %d columns need %zu bytes of shared memory, more than 200 KiB", q_rank, rank, rot, smem);
   auto go = [&](auto kernel, auto* out) {
-    ib::launch(kernel, (unsigned)T, 64, 0, stream, qd, P, (size_t)stride_p, row_len, q_rank, q_norm_w, out, c_norm_w, eps, cos_t, sin_t, rot_half, positions, seg_of_token,
-               *kv, rank, rot, status);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    ib::launch(kernel, (unsigned)T, 128, smem, stream, qd, P, (size_t)stride_p, row_len, q_rank, q_norm_w, out, c_norm_w, eps, cos_t, sin_t, rot_half, positions,
+               seg_of_token, *kv, rank, rot, status);
   };
   if (act_dtype == IB_F32 && kv->dtype == IB_F32) go(latent_down_kernel<float, float>, (float*)cq);
   else if (act_dtype == IB_BF16 && kv->dtype == IB_BF16) go(latent_down_kernel<__nv_bfloat16, __nv_bfloat16>, (__nv_bfloat16*)cq);

@@ -66,6 +66,7 @@ __global__ void qkv_conv_kernel(const float* __restrict__ proj, int P, size_t st
       if (row < t0) return old[(size_t)((taps - 1) + (row - t0)) * R + c];
       const float* src = proj + (size_t)row * R + c;
       float v = src[0];
+#pragma unroll 4
       for (int p = 1; p < P; p++) v += src[p * stride_p];
       return bias ? v + bias[c] : v;
     };
