@@ -495,6 +495,31 @@ def test_a_far_key_a_lost_state_row_and_a_left_out_bias_show(tmp_path):
         assert np.abs(off[20:] - want[20:]).max() / scale > 1e-2, change
 
 
+def test_a_left_out_gate_or_latent_norm_shows(tmp_path):
+    """One latent-attention layer whose gates are made decisive (their matrix scaled up, so a head is nearly open or nearly shut) and whose two
+    latent norms have weights far from one: the plain model with every gate half open, or with either norm's weights set to one, differs from the
+    right one by far more than the tolerance, and the engine matches the right one under portions and single tokens, in both precisions."""
+    mixer = {"heads": 3, "dim": 16, "vdim": 24, "kv_rank": 32, "q_rank": 40, "scale": 0.3, "mask": {"size": 21}}
+    cfg, w, write = _one_layer(tmp_path, "latent_attention", mixer, "gate", seed=78)
+    w["l0.mix.g"] = (w["l0.mix.g"].float() * 8).to(torch.bfloat16)
+    g = torch.Generator().manual_seed(3)
+    w["l0.mix.dq.norm"] = (0.3 + 2.0 * torch.rand((40,), generator=g)).to(torch.bfloat16)
+    w["l0.mix.dkv.norm"] = (0.3 + 2.0 * torch.rand((32,), generator=g)).to(torch.bfloat16)
+    toks = traces.prompt(13, 100, 64)
+    want = P.logits(toks, cfg, w).numpy()
+    scale = np.abs(want).max()
+    model = write()
+    for dtype, tol in (("float32", 1e-4), ("bfloat16", 6e-2)):
+        for steps in (traces.portions({"x": toks}), traces.tail_one_by_one({"x": toks}, tail=30)):
+            got = traces.run_steps(_runner(model, dtype, 128, 16), steps)
+            assert max(np.abs(row - want[pos]).max() for (_, pos), row in got.items()) / scale < tol
+    for name in ("l0.mix.g", "l0.mix.dq.norm", "l0.mix.dkv.norm"):
+        w2 = dict(w)
+        w2[name] = torch.zeros_like(w[name]) if name.endswith(".g") else torch.ones_like(w[name])
+        off = P.logits(toks, cfg, w2).numpy()
+        assert np.abs(off - want).max() / scale > 3e-2, name
+
+
 # ------------------------------------------------------------------------------------------ generation
 @pytest.mark.parametrize("name", list(td.CONFIGS))
 @pytest.mark.parametrize("graphs", [False, True])
