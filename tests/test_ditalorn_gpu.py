@@ -157,7 +157,7 @@ def test_output_norm_with_the_next_input_norm_and_embedding_with_positions(rt32,
 # ------------------------------------------------------------------------------------------ latent attention with a window
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,rank,page,window", [(6, 64, 16, 40), (3, 32, 16, 9), (5, 24, 8, 1), (8, 128, 32, 48), (4, 64, 64, 17), (2, 16, 16, 1000),
-                                                     (20, 48, 16, 33), (1, 256, 16, 64)])
+                                                     (20, 48, 16, 33), (1, 256, 16, 64), (4, 512, 16, 70), (2, 640, 16, 33)])
 def test_latent_attention_window_edges_in_portions_and_decoding(rt32, rt16, dtype, heads, rank, page, window):
     """Prompt portions that cross page borders and span more than a window, the first tokens of a sequence, and single decoded tokens (also cut
     into slices), all of one request on shuffled pages. One key stands out for one query: the oldest key inside the query's window and the one just
@@ -216,11 +216,12 @@ def test_latent_attention_window_edges_in_portions_and_decoding(rt32, rt16, dtyp
 # ------------------------------------------------------------------------------------------ attention with sigmoid weights
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim,page", [(4, 1, 64, 80, 16), (4, 2, 32, 16, 16), (5, 5, 24, 40, 8), (8, 2, 64, 128, 32), (16, 1, 32, 32, 64), (3, 1, 40, 24, 16),
-                                                          (6, 2, 128, 64, 16), (32, 1, 16, 16, 16)])
+                                                          (6, 2, 128, 64, 16), (32, 1, 16, 16, 16), (4, 2, 192, 256, 16), (2, 1, 256, 144, 16), (8, 2, 160, 64, 32)])
 def test_sigmoid_attention_far_keys_and_the_causal_edge(rt32, rt16, dtype, heads, kv_heads, dim, vdim, page):
     """Weights that are not normalised: a key far back that stands out adds its value with a weight near one whatever lies between, the key right
     after a query's position adds nothing, the distance bias and the bias per head move every weight. Prompt portions and single tokens cut into
-    slices, on shuffled pages. bfloat16 sizes that are multiples of 16 with up to 16 heads a kv head run on the tensor-core kernel."""
+    slices, on shuffled pages. bfloat16 sizes that are multiples of 16 with up to 16 heads a kv head run on the tensor-core kernels: prompt portions
+    with head sizes up to 128 on the one with sixteen rows a warp, larger heads and single tokens on the one that splits a tile's keys over the warps."""
     from inference_bench_b200.kernels import ops
     from inference_bench_b200.kernels.ops import KvLayerView
     rt = rt32 if dtype == torch.float32 else rt16
