@@ -156,7 +156,7 @@ def test_output_norm_with_the_next_input_norm_and_embedding_with_positions(rt32,
 
 # ------------------------------------------------------------------------------------------ latent attention with a window
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,rank,page,window", [(6, 64, 16, 40), (3, 32, 16, 9), (5, 24, 8, 1), (8, 128, 32, 48), (4, 64, 64, 17), (2, 16, 16, 1000),
+@pytest.mark.parametrize("heads,rank,page,window", [(6, 80, 16, 37), (3, 32, 16, 9), (5, 24, 8, 1), (8, 128, 32, 48), (4, 64, 64, 17), (2, 16, 16, 1000),
                                                      (20, 48, 16, 33), (1, 256, 16, 64), (4, 512, 16, 70), (2, 640, 16, 33)])
 def test_latent_attention_window_edges_in_portions_and_decoding(rt32, rt16, dtype, heads, rank, page, window):
     """Prompt portions that cross page borders and span more than a window, the first tokens of a sequence, and single decoded tokens (also cut
@@ -215,7 +215,7 @@ def test_latent_attention_window_edges_in_portions_and_decoding(rt32, rt16, dtyp
 
 # ------------------------------------------------------------------------------------------ attention with sigmoid weights
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,kv_heads,dim,vdim,page", [(4, 1, 64, 80, 16), (4, 2, 32, 16, 16), (5, 5, 24, 40, 8), (8, 2, 64, 128, 32), (16, 1, 32, 32, 64), (3, 1, 40, 24, 16),
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,page", [(8, 2, 48, 80, 16), (4, 2, 32, 16, 16), (5, 5, 24, 40, 8), (8, 2, 64, 128, 32), (16, 1, 32, 32, 64), (3, 1, 40, 24, 16),
                                                           (6, 2, 128, 64, 16), (32, 1, 16, 16, 16), (4, 2, 192, 256, 16), (2, 1, 256, 144, 16), (8, 2, 160, 64, 32)])
 def test_sigmoid_attention_far_keys_and_the_causal_edge(rt32, rt16, dtype, heads, kv_heads, dim, vdim, page):
     """Weights that are not normalised: a key far back that stands out adds its value with a weight near one whatever lies between, the key right
@@ -280,7 +280,7 @@ LENS = {"a": 23, "b": 9, "c": 16}     # b ends after the fourth step; c takes it
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,kv_heads,dim,vdim,taps,every", [(4, 1, 64, 80, 3, 4), (4, 2, 32, 16, 4, 5), (5, 5, 24, 40, 1, 0), (2, 1, 16, 48, 2, 1), (3, 1, 40, 24, 6, 7)])
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,taps,every", [(6, 2, 48, 80, 3, 4), (4, 2, 32, 16, 4, 5), (5, 5, 24, 40, 1, 0), (2, 1, 16, 48, 2, 1), (3, 1, 40, 24, 6, 7)])
 def test_convolution_of_projections_over_portions_and_slots(rt32, rt16, dtype, heads, kv_heads, dim, vdim, taps, every):
     """Three requests in two slots (the third uses the second's again), portions of 1, 2 and more tokens beside one another: every row of q and
     every cached k and v equals the plain convolution of the whole sequence, with the temperature and the value norm."""
